@@ -1,0 +1,89 @@
+/*
+ * C ABI of libtriturus_b200.so: the log-space contraction hot path of triturus (lm2exp, lt2exp) as
+ * hand-written sm_100a CUDA.  Plain pointers and sizes only; no torch types cross this boundary.
+ *
+ * All tensor pointers are DEVICE pointers to fp32 data on the device that is current when the call is
+ * made.  Strides are in elements.  The innermost stride of every tensor must be 1, every other stride a
+ * multiple of 4 elements and every base pointer 16-byte aligned (TMA rules); callers that cannot meet this
+ * make a padded copy first (the Python wrappers do).  The library allocates nothing: the output, the
+ * workspace and the status word belong to the caller.  Calls are asynchronous on `stream` and never
+ * synchronise; they are re-entrant and may run concurrently on different streams or devices as long as
+ * each in-flight call has its own workspace and output.
+ *
+ * Return value: 0 on success or a negative TRITURUS_B200_E* code; nothing is thrown and the process is
+ * never terminated.  Device-side protocol time-outs (bounded waits inside the kernels) are reported
+ * through `status_dev` (a zero-initialised int32 in device memory, may be NULL): it stays 0 on success and
+ * receives a positive code otherwise, readable after the stream has been synchronised.
+ */
+#ifndef TRITURUS_B200_H
+#define TRITURUS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRITURUS_B200_OK 0
+#define TRITURUS_B200_EINVAL (-1)      /* bad shape, NULL pointer, unknown precision or variant */
+#define TRITURUS_B200_EALIGN (-2)      /* pointer or stride violates the alignment rules above */
+#define TRITURUS_B200_EWORKSPACE (-3)  /* workspace too small */
+#define TRITURUS_B200_ETENSORMAP (-4)  /* the driver rejected a tensor map */
+#define TRITURUS_B200_ELAUNCH (-5)     /* kernel launch or attribute call failed */
+#define TRITURUS_B200_EDRIVER (-6)     /* driver entry point unavailable */
+
+#define TRITURUS_B200_PRECISION_TF32 0   /* one tf32 MMA pass; triturus.utils.set_tf32_enabled(True) */
+#define TRITURUS_B200_PRECISION_3XTF32 1 /* hi/lo split, ~fp32 accuracy; set_tf32_enabled(False) */
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int triturus_b200_version(void);
+
+/* Human-readable text for a negative return code or a positive status word. */
+const char* triturus_b200_strerror(int code);
+
+/*
+ * lm2exp: out[r,i,k] = log sum_j a[r,i,j] * exp(b[r,j,k]), stabilised by the clamped column maximum of b
+ * so that a column of b that is entirely -inf yields -inf.
+ * Replaces triturus/lm2exp.py:167-206 (host wrapper) and :63-164 (_ker_lm2exp); semantics follow
+ * baselines/lm2exp.py:4-14.
+ *   a [R,I,J], b [R,J,K], out [R,I,K]; *_strides = element strides of the three dimensions.
+ *   precision: TRITURUS_B200_PRECISION_*.
+ *   variant:   0 = choose the tile shape from the problem size; otherwise BN * 10 + MT with
+ *              BN in {128, 256} output columns and MT in {1, 2} 128-row blocks per CTA tile
+ *              (the counterpart of the reference's autotune table, triturus/lm2exp.py:7-58).
+ *   workspace: at least triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned; holds the
+ *              [R,K] stabiliser.
+ */
+size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K);
+int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+                             const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                             int precision, int variant, void* workspace, size_t workspace_bytes,
+                             int32_t* status_dev, void* stream);
+
+/*
+ * lt2exp: out[r,s,k] = log sum_{i,j} w[r,s,i,j] * exp(a[r,i,k]) * exp(b[r,j,k]), stabilised by the clamped
+ * column maxima of a and b.
+ * Replaces triturus/lt2exp.py:519-630 (host wrapper), :227-357 (_ker_lt2exp_unsplit) and :365-506
+ * (_ker_lt2exp_split); semantics follow baselines/lt2exp.py:4-25.
+ *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].
+ *   variant: 0 = automatic, otherwise BN * 10 + MT as above.
+ *   No workspace is needed.
+ */
+int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
+                             int64_t I, int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
+                             const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
+                             int32_t* status_dev, void* stream);
+
+/*
+ * The stabiliser alone: m[r,k] = clamp(max_j x[r,j,k], -1e38, 1e38), m contiguous [R,K].
+ * This is the pre-pass of triturus/lm2exp.py:125-127 (and baselines/lm2exp.py:11-12) as its own launch.
+ */
+int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
+                             void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TRITURUS_B200_H */

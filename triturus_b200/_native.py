@@ -1,0 +1,217 @@
+"""ctypes binding of libtriturus_b200.so and its registration as torch custom ops.
+
+The shared library is the product: there is no Python, Triton or CPU fallback behind these functions.  If
+the library cannot be loaded the import fails loudly, and calling an op with tensors that are not on a
+CUDA device raises.
+"""
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+from . import build as _build
+
+PRECISION_TF32 = 0
+PRECISION_3XTF32 = 1
+
+EXPORTED_SYMBOLS = (
+    "triturus_b200_version",
+    "triturus_b200_strerror",
+    "triturus_b200_lm2exp_workspace_bytes",
+    "triturus_b200_lm2exp_f32",
+    "triturus_b200_lt2exp_f32",
+    "triturus_b200_colmax_f32",
+)
+
+
+class NativeLibraryError(RuntimeError):
+    """The shared library is missing, cannot be loaded, or returned an error code."""
+
+
+def _load() -> ctypes.CDLL:
+    path = _build.LIB_PATH
+    if not path.exists():
+        # First use in a fresh checkout: build in-tree.  A failure here is fatal by design.
+        try:
+            _build.build()
+        except Exception as exc:  # noqa: BLE001
+            raise NativeLibraryError(
+                f"{path} is missing and could not be built ({exc}); run `python -m triturus_b200.build`"
+            ) from exc
+    try:
+        lib = ctypes.CDLL(os.fspath(path))
+    except OSError as exc:
+        raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
+
+    i64p = POINTER(c_int64)
+    lib.triturus_b200_version.restype = c_int
+    lib.triturus_b200_version.argtypes = []
+    lib.triturus_b200_strerror.restype = c_char_p
+    lib.triturus_b200_strerror.argtypes = [c_int]
+    lib.triturus_b200_lm2exp_workspace_bytes.restype = c_size_t
+    lib.triturus_b200_lm2exp_workspace_bytes.argtypes = [c_int64] * 4
+    lib.triturus_b200_lm2exp_f32.restype = c_int
+    lib.triturus_b200_lm2exp_f32.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
+        c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_lt2exp_f32.restype = c_int
+    lib.triturus_b200_lt2exp_f32.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+        i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_colmax_f32.restype = c_int
+    lib.triturus_b200_colmax_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, i64p, c_void_p]
+    return lib
+
+
+LIB = _load()
+
+
+def strerror(code: int) -> str:
+    return LIB.triturus_b200_strerror(int(code)).decode()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeLibraryError(f"{what} failed with code {rc}: {strerror(rc)}")
+
+
+def _i64(vals) -> ctypes.Array:
+    return (c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise NativeLibraryError(
+                "triturus_b200 ops run only on CUDA tensors (sm_100a); there is no CPU implementation"
+            )
+
+
+# One zero-initialised status word per device, shared by all launches on it.  A kernel writes a positive
+# code there only when one of its bounded waits gives up; `check_status` reads it back.
+_STATUS = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _STATUS.get(idx)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _STATUS[idx] = st
+    return st
+
+
+def check_status(device=None) -> None:
+    """Synchronise `device` and raise if any kernel launched through this module reported a time-out."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    elif isinstance(device, int):
+        device = torch.device("cuda", device)
+    st = _status_word(device)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise NativeLibraryError(f"device-side failure {code}: {strerror(code)}")
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Return `t` or a padded copy whose innermost stride is 1, other strides multiples of 4 elements and
+    base 16-byte aligned (what a TMA tensor map needs).  The logical shape is unchanged."""
+    ok = t.data_ptr() % 16 == 0 and (t.shape[-1] == 1 or t.stride(-1) == 1)
+    if ok:
+        for d in range(t.dim() - 1):
+            if t.shape[d] > 1 and (t.stride(d) <= 0 or t.stride(d) % 4 != 0):
+                ok = False
+                break
+    if ok:
+        return t
+    inner = t.shape[-1]
+    padded = (inner + 3) // 4 * 4
+    buf = torch.empty(*t.shape[:-1], padded, dtype=t.dtype, device=t.device)
+    view = buf[..., :inner]
+    view.copy_(t)
+    return view
+
+
+def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """Return `t` or a contiguous copy when its innermost stride is not 1 or a stride is not positive."""
+    if (t.shape[-1] == 1 or t.stride(-1) == 1) and all(
+        t.shape[d] == 1 or t.stride(d) > 0 for d in range(t.dim() - 1)
+    ):
+        return t
+    return t.contiguous()
+
+
+def colmax(x: torch.Tensor) -> torch.Tensor:
+    """Clamped column maximum of x[R, J, K] over J -> [R, K] (the stabiliser pre-pass)."""
+    _require_cuda(x)
+    x = _inner_contiguous(x)
+    R, J, K = x.shape
+    m = torch.empty((R, K), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        rc = LIB.triturus_b200_colmax_f32(x.data_ptr(), m.data_ptr(), R, J, K, _i64(x.stride()), stream)
+    _check(rc, "triturus_b200_colmax_f32")
+    return m
+
+
+def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
+    _require_cuda(a, b)
+    R, I, J = a.shape
+    K = b.shape[2]
+    a = _tma_ready(a)
+    b = _tma_ready(b)
+    out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
+    ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
+    ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        rc = LIB.triturus_b200_lm2exp_f32(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K,
+            _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
+            int(precision), int(variant), ws.data_ptr(), ws_bytes,
+            _status_word(a.device).data_ptr(), stream,
+        )  # fmt: skip
+    _check(rc, "triturus_b200_lm2exp_f32")
+    return out
+
+
+def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
+    _require_cuda(w, a, b)
+    R, S, I, J = w.shape
+    K = a.shape[2]
+    w = _tma_ready(w)
+    a = _inner_contiguous(a)
+    b = _inner_contiguous(b)
+    out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        rc = LIB.triturus_b200_lt2exp_f32(
+            w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), R, S, I, J, K,
+            _i64(w.stride()), _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
+            int(precision), int(variant), _status_word(a.device).data_ptr(), stream,
+        )  # fmt: skip
+    _check(rc, "triturus_b200_lt2exp_f32")
+    return out
+
+
+# ---------------------------------------------------------------------------- torch custom ops
+# torch.ops.triturus.lm2exp / torch.ops.triturus.lt2exp: CUDA only, with shape-inferring fake kernels so
+# the ops trace under torch.compile / FakeTensor.  The reference defines no autograd for these ops.
+
+lm2exp_op = torch.library.custom_op("triturus::lm2exp", _lm2exp_impl, mutates_args=(), device_types="cuda")
+lt2exp_op = torch.library.custom_op("triturus::lt2exp", _lt2exp_impl, mutates_args=(), device_types="cuda")
+
+
+@lm2exp_op.register_fake
+def _lm2exp_fake(a, b, precision, variant):
+    return a.new_empty((a.shape[0], a.shape[1], b.shape[2]))
+
+
+@lt2exp_op.register_fake
+def _lt2exp_fake(w, a, b, precision, variant):
+    return a.new_empty((w.shape[0], w.shape[1], a.shape[2]))

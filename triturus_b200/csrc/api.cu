@@ -1,0 +1,414 @@
+// extern "C" boundary of libtriturus_b200.so: argument validation, tensor-map encoding, tile-shape
+// selection and kernel launches.  Declarations and the reference interfaces they replace are in
+// include/triturus_b200.h.  Nothing here allocates device memory or synchronises.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include <mutex>
+
+#include "../../include/triturus_b200.h"
+#include "lm2exp_kernel.cuh"
+#include "lt2exp_kernel.cuh"
+
+namespace tb200 {
+
+// ----------------------------------------------------------------------------- stabiliser pre-pass
+
+// m[r,k] = clamp(max_j x[r,j,k]).  One block owns 32 columns of one batch entry; its 8 warps split the
+// rows.  In the vector path a warp reads 4 rows x 128 bytes per step (lane = 4 * row + float4 group) and
+// folds the four row slots with warp shuffles.
+template <bool VEC>
+__global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
+                                                      int64_t s0, int64_t s1) {
+  __shared__ float part[8][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.y;
+  const int c0 = blockIdx.x * 32;
+  const float* xb = x + static_cast<int64_t>(r) * s0;
+  if (VEC) {
+    const int cg = lane & 7, rs = lane >> 3;
+    const int c = c0 + cg * 4;
+    float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    if (c < K) {  // K % 4 == 0 in this path, so the float4 is entirely inside the row
+      for (int j = warp * 4 + rs; j < J; j += 32) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(xb + static_cast<int64_t>(j) * s1 + c));
+        mx.x = fmaxf(mx.x, v.x);
+        mx.y = fmaxf(mx.y, v.y);
+        mx.z = fmaxf(mx.z, v.z);
+        mx.w = fmaxf(mx.w, v.w);
+      }
+    }
+#pragma unroll
+    for (int sh = 8; sh <= 16; sh <<= 1) {
+      mx.x = fmaxf(mx.x, __shfl_xor_sync(0xffffffffu, mx.x, sh));
+      mx.y = fmaxf(mx.y, __shfl_xor_sync(0xffffffffu, mx.y, sh));
+      mx.z = fmaxf(mx.z, __shfl_xor_sync(0xffffffffu, mx.z, sh));
+      mx.w = fmaxf(mx.w, __shfl_xor_sync(0xffffffffu, mx.w, sh));
+    }
+    if (rs == 0) {
+      part[warp][cg * 4 + 0] = mx.x;
+      part[warp][cg * 4 + 1] = mx.y;
+      part[warp][cg * 4 + 2] = mx.z;
+      part[warp][cg * 4 + 3] = mx.w;
+    }
+  } else {
+    const int c = c0 + lane;
+    float mx = -INFINITY;
+    if (c < K) {
+      for (int j = warp; j < J; j += 8) mx = fmaxf(mx, __ldg(xb + static_cast<int64_t>(j) * s1 + c));
+    }
+    part[warp][lane] = mx;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float mx = part[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, part[w][lane]);
+    const int c = c0 + lane;
+    if (c < K) m[static_cast<int64_t>(r) * K + c] = clamp_stab(mx);
+  }
+}
+
+// ----------------------------------------------------------------------------- driver entry point for tensor maps
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// fp32 tensor map of rank `rank`; dims/strides listed innermost first, strides in elements
+// (strides[0] is the innermost stride and must be 1).
+static int make_tmap(CUtensorMap* out, const float* base, int rank, const int64_t* dims, const int64_t* strides,
+                     const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return TRITURUS_B200_EDRIVER;
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bx[5], es[5];
+  for (int d = 0; d < rank; ++d) {
+    gdim[d] = static_cast<cuuint64_t>(dims[d]);
+    bx[d] = box[d];
+    es[d] = 1;
+    if (d > 0) gstr[d - 1] = static_cast<cuuint64_t>(strides[d]) * sizeof(float);
+  }
+  const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, static_cast<cuuint32_t>(rank),
+                         const_cast<float*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? TRITURUS_B200_OK : TRITURUS_B200_ETENSORMAP;
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// A stride is usable by TMA when it is a positive multiple of 4 elements; strides of size-1 dimensions
+// are irrelevant and get a safe value instead.
+static bool fix_stride(int64_t size, int64_t& stride, int64_t natural) {
+  if (size == 1) {
+    stride = natural;
+    return true;
+  }
+  return stride > 0 && (stride & 3) == 0;
+}
+
+static int64_t round_up4(int64_t v) { return (v + 3) & ~int64_t(3); }
+
+// ----------------------------------------------------------------------------- lm2exp launch
+
+template <class Cfg>
+static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expParams p, cudaStream_t stream) {
+  auto kern = lm2exp_kernel<Cfg>;
+  static std::once_flag once[64];
+  static cudaError_t attr_rc[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
+  std::call_once(once[dev], [&] {
+    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  });
+  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  p.tiles_m = (p.I + Cfg::BM * Cfg::MT - 1) / (Cfg::BM * Cfg::MT);
+  p.tiles_n = (p.K + Cfg::BN - 1) / Cfg::BN;
+  const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
+  if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
+  p.num_tiles = static_cast<int>(nt);
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+}
+
+//                          BN   MT PREC NS NR NTW
+using LmT_128_1 = Lm2expCfg<128, 1, 0, 4, 3, 8>;
+using LmT_128_2 = Lm2expCfg<128, 2, 0, 3, 3, 8>;
+using LmT_256_1 = Lm2expCfg<256, 1, 0, 3, 2, 8>;
+using LmT_256_2 = Lm2expCfg<256, 2, 0, 2, 2, 8>;
+using LmX_128_1 = Lm2expCfg<128, 1, 1, 2, 2, 8>;
+using LmX_128_2 = Lm2expCfg<128, 2, 1, 2, 2, 8>;
+
+static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt) {
+  return R * ((rows + 128 * mt - 1) / (128 * mt)) * ((cols + bn - 1) / bn);
+}
+
+// Largest tile that still gives every SM at least one tile; otherwise the smallest tile.
+static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256) {
+  const int sms = sm_count();
+  const int mt_max = rows > 128 ? 2 : 1;
+  const int bn_max = (cols > 128 && allow_bn256) ? 256 : 128;
+  if (tile_count(R, rows, cols, bn_max, mt_max) >= sms) return bn_max * 10 + mt_max;
+  if (bn_max == 256 && tile_count(R, rows, cols, 128, mt_max) >= sms) return 128 * 10 + mt_max;
+  if (mt_max == 2 && tile_count(R, rows, cols, bn_max, 1) >= sms) return bn_max * 10 + 1;
+  return 128 * 10 + 1;
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" {
+
+int triturus_b200_version(void) { return 100; }
+
+const char* triturus_b200_strerror(int code) {
+  switch (code) {
+    case TRITURUS_B200_OK: return "ok";
+    case TRITURUS_B200_EINVAL: return "invalid argument (shape, pointer, precision or variant)";
+    case TRITURUS_B200_EALIGN: return "pointer or stride violates the 16-byte alignment rules";
+    case TRITURUS_B200_EWORKSPACE: return "workspace too small or misaligned";
+    case TRITURUS_B200_ETENSORMAP: return "tensor map rejected by the driver";
+    case TRITURUS_B200_ELAUNCH: return "kernel launch failed";
+    case TRITURUS_B200_EDRIVER: return "cuTensorMapEncodeTiled unavailable";
+    case STATUS_TIMEOUT_PRODUCER: return "device: TMA producer wait timed out";
+    case STATUS_TIMEOUT_TRANSFORM: return "device: transform warp wait timed out";
+    case STATUS_TIMEOUT_MMA: return "device: MMA issuer wait timed out";
+    case STATUS_TIMEOUT_EPILOGUE: return "device: epilogue wait timed out";
+    case STATUS_TIMEOUT_SETUP: return "device: setup wait timed out";
+    default: return "unknown code";
+  }
+}
+
+int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
+                             void* stream) {
+  if (x == nullptr || m == nullptr || x_strides == nullptr) return TRITURUS_B200_EINVAL;
+  if (R <= 0 || J <= 0 || K <= 0 || R > 65535 || J > INT32_MAX || K > INT32_MAX) return TRITURUS_B200_EINVAL;
+  if (K > 1 && x_strides[2] != 1) return TRITURUS_B200_EALIGN;
+  const bool vec = (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
+  const dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(R));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec) {
+    colmax_kernel<true><<<grid, 256, 0, st>>>(x, m, static_cast<int>(J), static_cast<int>(K), x_strides[0],
+                                             x_strides[1]);
+  } else {
+    colmax_kernel<false><<<grid, 256, 0, st>>>(x, m, static_cast<int>(J), static_cast<int>(K), x_strides[0],
+                                              x_strides[1]);
+  }
+  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+}
+
+size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K) {
+  (void)I;
+  (void)J;
+  if (R <= 0 || K <= 0) return 0;
+  return static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float);
+}
+
+int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+                             const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                             int precision, int variant, void* workspace, size_t workspace_bytes,
+                             int32_t* status_dev, void* stream) {
+  if (a == nullptr || b == nullptr || out == nullptr || a_strides == nullptr || b_strides == nullptr ||
+      out_strides == nullptr)
+    return TRITURUS_B200_EINVAL;
+  if (R <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (R > 65535 || I > (1 << 30) || J > (1 << 30) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  if (workspace == nullptr || workspace_bytes < triturus_b200_lm2exp_workspace_bytes(R, I, J, K) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return TRITURUS_B200_EWORKSPACE;
+
+  int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
+  int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
+  int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
+  if ((J > 1 && as2 != 1) || (K > 1 && bs2 != 1) || (K > 1 && os2 != 1)) return TRITURUS_B200_EALIGN;
+  if (!aligned16(a) || !aligned16(b)) return TRITURUS_B200_EALIGN;
+  if (!fix_stride(I, as1, round_up4(J)) || !fix_stride(R, as0, round_up4(J) * I)) return TRITURUS_B200_EALIGN;
+  if (!fix_stride(J, bs1, round_up4(K)) || !fix_stride(R, bs0, round_up4(K) * J)) return TRITURUS_B200_EALIGN;
+  if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
+  if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
+
+  if (variant == 0) variant = auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  const int bn = variant / 10, mt = variant % 10;
+  if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
+  const int bn_eff = (precision == TRITURUS_B200_PRECISION_3XTF32) ? 128 : bn;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* m_ws = static_cast<float*>(workspace);
+  const int64_t bstr[3] = {bs0, bs1, 1};
+  int rc = triturus_b200_colmax_f32(b, m_ws, R, J, K, bstr, stream);
+  if (rc != TRITURUS_B200_OK) return rc;
+
+  CUtensorMap ta, tb;
+  {
+    const int64_t dims[3] = {J, I, R};
+    const int64_t strides[3] = {1, as1, as0};
+    const uint32_t box[3] = {32, 128, 1};
+    rc = make_tmap(&ta, a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  {
+    const int64_t dims[3] = {K, J, R};
+    const int64_t strides[3] = {1, bs1, bs0};
+    const uint32_t box[3] = {static_cast<uint32_t>(bn_eff), 32, 1};
+    rc = make_tmap(&tb, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+
+  Lm2expParams p;
+  p.m_ws = m_ws;
+  p.out = out;
+  p.out_s0 = os0;
+  p.out_s1 = os1;
+  p.R = static_cast<int>(R);
+  p.I = static_cast<int>(I);
+  p.J = static_cast<int>(J);
+  p.K = static_cast<int>(K);
+  p.tiles_m = p.tiles_n = p.num_tiles = 0;
+  p.status = status_dev;
+
+  if (precision == TRITURUS_B200_PRECISION_3XTF32) {
+    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, p, st);
+  }
+  if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, p, st);
+  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, p, st);
+}
+
+}  // extern "C"
+
+// ----------------------------------------------------------------------------- lt2exp launch
+
+namespace tb200 {
+
+template <class Cfg>
+static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, cudaStream_t stream) {
+  auto kern = lt2exp_kernel<Cfg>;
+  static std::once_flag once[64];
+  static cudaError_t attr_rc[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
+  std::call_once(once[dev], [&] {
+    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  });
+  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  p.tiles_m = (p.S + Cfg::BM * Cfg::MT - 1) / (Cfg::BM * Cfg::MT);
+  p.tiles_n = (p.K + Cfg::BN - 1) / Cfg::BN;
+  const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
+  if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
+  p.num_tiles = static_cast<int>(nt);
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tw, p);
+  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+}
+
+//                          BN   MT PREC NS NTW
+using LtT_128_1 = Lt2expCfg<128, 1, 0, 6, 8>;
+using LtT_128_2 = Lt2expCfg<128, 2, 0, 4, 8>;
+using LtT_256_1 = Lt2expCfg<256, 1, 0, 4, 8>;
+using LtT_256_2 = Lt2expCfg<256, 2, 0, 3, 8>;
+using LtX_128_1 = Lt2expCfg<128, 1, 1, 3, 8>;
+using LtX_128_2 = Lt2expCfg<128, 2, 1, 2, 8>;
+using LtX_256_1 = Lt2expCfg<256, 1, 1, 2, 8>;
+
+}  // namespace tb200
+
+extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
+                                        int64_t S, int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
+                                        const int64_t a_strides[3], const int64_t b_strides[3],
+                                        const int64_t out_strides[3], int precision, int variant,
+                                        int32_t* status_dev, void* stream) {
+  if (w == nullptr || a == nullptr || b == nullptr || out == nullptr || w_strides == nullptr ||
+      a_strides == nullptr || b_strides == nullptr || out_strides == nullptr)
+    return TRITURUS_B200_EINVAL;
+  if (R <= 0 || S <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (R > 65535 || S > (1 << 30) || I > (1 << 24) || J > (1 << 24) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
+  if (((J + 31) / 32) * I > (1 << 28)) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+
+  int64_t ws0 = w_strides[0], ws1 = w_strides[1], ws2 = w_strides[2], ws3 = w_strides[3];
+  int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
+  int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
+  int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
+  if ((J > 1 && ws3 != 1) || (K > 1 && (as2 != 1 || bs2 != 1 || os2 != 1))) return TRITURUS_B200_EALIGN;
+  if (!aligned16(w)) return TRITURUS_B200_EALIGN;
+  const int64_t j4 = round_up4(J);
+  if (!fix_stride(I, ws2, j4) || !fix_stride(S, ws1, j4 * I) || !fix_stride(R, ws0, j4 * I * S))
+    return TRITURUS_B200_EALIGN;
+  if ((I > 1 && as1 <= 0) || (R > 1 && as0 <= 0) || (J > 1 && bs1 <= 0) || (R > 1 && bs0 <= 0) ||
+      (S > 1 && os1 <= 0) || (R > 1 && os0 <= 0))
+    return TRITURUS_B200_EALIGN;
+
+  if (variant == 0) variant = auto_variant(R, S, K, true);
+  const int bn = variant / 10, mt = variant % 10;
+  if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
+
+  CUtensorMap tw;
+  {
+    const int64_t dims[4] = {J, I, S, R};
+    const int64_t strides[4] = {1, ws2, ws1, ws0};
+    const uint32_t box[4] = {32, 1, 128, 1};
+    const int rc = make_tmap(&tw, w, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+
+  Lt2expParams p;
+  p.a = a;
+  p.b = b;
+  p.out = out;
+  p.a_s0 = as0;
+  p.a_s1 = as1;
+  p.b_s0 = bs0;
+  p.b_s1 = bs1;
+  p.out_s0 = os0;
+  p.out_s1 = os1;
+  p.R = static_cast<int>(R);
+  p.S = static_cast<int>(S);
+  p.I = static_cast<int>(I);
+  p.J = static_cast<int>(J);
+  p.K = static_cast<int>(K);
+  p.tiles_m = p.tiles_n = p.num_tiles = 0;
+  p.status = status_dev;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (precision == TRITURUS_B200_PRECISION_3XTF32) {
+    if (bn == 256 && mt == 1) return launch_lt2exp<LtX_256_1>(tw, p, st);
+    return mt == 2 ? launch_lt2exp<LtX_128_2>(tw, p, st) : launch_lt2exp<LtX_128_1>(tw, p, st);
+  }
+  if (bn == 256) return mt == 2 ? launch_lt2exp<LtT_256_2>(tw, p, st) : launch_lt2exp<LtT_256_1>(tw, p, st);
+  return mt == 2 ? launch_lt2exp<LtT_128_2>(tw, p, st) : launch_lt2exp<LtT_128_1>(tw, p, st);
+}

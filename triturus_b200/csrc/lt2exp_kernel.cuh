@@ -1,0 +1,394 @@
+// lt2exp:  out[r,s,k] = ma[r,k] + mb[r,k] + log( sum_{i,j} w[r,s,i,j] * exp(a[r,i,k]-ma[r,k]) * exp(b[r,j,k]-mb[r,k]) )
+//
+// Replaces the reference's Triton kernels _ker_lt2exp_unsplit / _ker_lt2exp_split
+// (triturus/lt2exp.py:227-357, 365-506) with one persistent, warp-specialised sm_100a kernel.
+// As a GEMM: D[M = s, N = k] = W[M, Kc = (i,j)] * P[Kc, N] with the Khatri-Rao operand
+// P[(i,j), k] = exp(a[i,k]-ma[k]) * exp(b[j,k]-mb[k]), which is generated tile by tile in shared memory and
+// never written to HBM (the reference's torch baseline materialises it, baselines/lt2exp.py:21-22, and its
+// Triton kernels recompute both exps for every (i,j) pair, triturus/lt2exp.py:337-338).
+//
+// One k-block of the contraction is one i and 32 consecutive j (a 128-byte row segment of w), fetched by a
+// 4-D TMA box {32 j, 1 i, 128 s, 1 r} with the 128-byte swizzle; j past J is zero-filled.  k-blocks run with
+// the j-chunk outermost so a transform thread keeps its 32 exp(b - mb) values in registers for I k-blocks
+// and needs one exp(a - ma) per k-block, prefetched from global memory eight k-blocks ahead.
+//
+//   warp 0      TMA producer (w tiles).
+//   warp 1      TMEM allocation; one lane issues tcgen05.mma.kind::tf32 and commits.
+//   warps 4-7   epilogue: out = (ma + mb) + log(acc).
+//   warps 8+    transform: column maxima of a and b (-inf safe), then the P operand of every k-block.
+//               The NTT / BN thread groups take alternate k-blocks.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace tb200 {
+
+struct Lt2expParams {
+  const float* a;  // [R, I, K]
+  const float* b;  // [R, J, K]
+  float* out;      // [R, S, K]
+  int64_t a_s0, a_s1, b_s0, b_s1;  // element strides (innermost stride is 1)
+  int64_t out_s0, out_s1;
+  int R, S, I, J, K;
+  int tiles_m, tiles_n, num_tiles;
+  int* status;
+};
+
+template <int BN_, int MT_, int PREC_, int NS_, int NTW_>
+struct Lt2expCfg {
+  static constexpr int BM = 128, BK = 32;
+  static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_, NTW = NTW_;
+  static constexpr int NCOPY = PREC ? 2 : 1;
+  static constexpr int A_TILE = BM * BK * 4;
+  static constexpr int B_TILE = BN * BK * 4;
+  static constexpr int STAGE = NCOPY * (MT * A_TILE + B_TILE);
+  static constexpr int ACC_COLS = MT * BN;
+  static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
+  static constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256 ? 256 : 512);
+  static constexpr int NTHREADS = (8 + NTW) * 32;
+  static constexpr int NTT = NTW * 32;
+  static constexpr int NGROUPS = NTT / BN;      // transform thread groups taking alternate k-blocks
+  static constexpr int GROUP_WARPS = BN / 32;
+  static constexpr int NBAR = 3 * NS + 6;
+  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + 2 * BN * 4 + NBAR * 8 + 64;
+  static_assert(NTT % BN == 0 && NGROUPS >= 1, "transform thread mapping");
+  static_assert(NBUF * ACC_COLS <= 512, "TMEM capacity");
+  static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
+};
+
+// max over `rows` elements `stride` apart, sixteen loads in flight.
+__device__ __forceinline__ float column_max(const float* col, int64_t stride, int rows) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+  int i = 0;
+  for (; i + 16 <= rows; i += 16) {
+    float v[16];
+#pragma unroll
+    for (int x = 0; x < 16; ++x) v[x] = __ldg(col + static_cast<int64_t>(i + x) * stride);
+#pragma unroll
+    for (int x = 0; x < 16; x += 4) {
+      m0 = fmaxf(m0, v[x]);
+      m1 = fmaxf(m1, v[x + 1]);
+      m2 = fmaxf(m2, v[x + 2]);
+      m3 = fmaxf(m3, v[x + 3]);
+    }
+  }
+  for (; i < rows; ++i) m0 = fmaxf(m0, __ldg(col + static_cast<int64_t>(i) * stride));
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::NTHREADS, 1)
+lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) {
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS;
+  constexpr int PREC = Cfg::PREC;
+  constexpr int PF = 8;  // prefetch distance (own k-blocks) for the a values
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  float* msum = reinterpret_cast<float*>(smem + NS * Cfg::STAGE);  // [2][BN]: ma + mb of the tile's columns
+  uint64_t* bars = reinterpret_cast<uint64_t*>(msum + 2 * BN);
+  uint64_t* a_full = bars;               // [NS] w tiles landed
+  uint64_t* b_full = bars + NS;          // [NS] P operand (and w split) written
+  uint64_t* opnd_empty = bars + 2 * NS;  // [NS] MMAs reading the stage retired
+  uint64_t* acc_full = bars + 3 * NS;    // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint64_t* msum_empty = acc_empty + 2;  // [2] epilogue finished reading msum[slot]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(msum_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortCtl ctl{abort_flag, p.status};
+
+  auto a_tile = [&](int s, int c, int t) -> uint8_t* {
+    return stage_base + s * Cfg::STAGE + (c * MT + t) * Cfg::A_TILE;
+  };
+  auto b_tile = [&](int s, int c) -> uint8_t* {
+    return stage_base + s * Cfg::STAGE + Cfg::NCOPY * MT * Cfg::A_TILE + c * Cfg::B_TILE;
+  };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&b_full[s], Cfg::GROUP_WARPS);
+      mbar_init(&opnd_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 4);
+      mbar_init(&msum_empty[s], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int JC = (p.J + BK - 1) / BK;  // j-chunks
+  const int KB = JC * p.I;             // k-blocks per tile: (jc, i), i fastest
+
+  auto decode = [&](int tile, int& r, int& n0, int& s0) {
+    const int tm = tile % p.tiles_m;
+    const int rest = tile / p.tiles_m;
+    const int tn = rest % p.tiles_n;
+    r = rest / p.tiles_n;
+    n0 = tn * BN;
+    s0 = tm * (BM * MT);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int r, n0, s0;
+        decode(tile, r, n0, s0);
+        for (int jc = 0; ok && jc < JC; ++jc) {
+          for (int i = 0; i < p.I; ++i, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
+            if (!(ok = mbar_wait(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
+            mbar_arrive_expect_tx(&a_full[s], MT * Cfg::A_TILE);
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+              tma_load_4d(a_tile(s, 0, t), &tmap_w, &a_full[s], jc * BK, i, s0 + t * BM, r);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+        const int buf = tcount % Cfg::NBUF;
+        const uint32_t aph = (tcount / Cfg::NBUF) & 1;
+        if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
+        tc_fence_after_sync();
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!(ok = mbar_wait(&a_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+          if (!(ok = mbar_wait(&b_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+          tc_fence_after_sync();
+          const uint64_t db_hi = umma_desc_k_sw128(smem_u32(b_tile(s, 0)));
+          const uint64_t db_lo = PREC ? umma_desc_k_sw128(smem_u32(b_tile(s, 1))) : 0;
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
+            const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
+            const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks) {
+              const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+              if (PREC) {
+                umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 2 * ks, idesc, acc);
+                umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 2 * ks, idesc, 1u);
+                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, 1u);
+              } else {
+                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, acc);
+              }
+            }
+          }
+          umma_commit(&opnd_empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const bool vec_ok = ((p.K & 3) == 0) && ((p.out_s1 & 3) == 0) && ((p.out_s0 & 3) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      int r, n0, s0;
+      decode(tile, r, n0, s0);
+      const int buf = tcount % Cfg::NBUF;
+      const uint32_t aph = (tcount / Cfg::NBUF) & 1;
+      const int slot = tcount & 1;
+      if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int t = 0; t < MT; ++t) {
+        if (s0 + t * BM >= p.S) break;
+        const int row = s0 + t * BM + q * 32 + lane;
+        float* out_row = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(row) * p.out_s1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int k0 = n0 + c * 32;
+          if (k0 >= p.K) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
+          const float m_lane = msum[slot * BN + c * 32 + lane];
+          tmem_ld_wait();
+          float o[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float m_e = __shfl_sync(0xffffffffu, m_lane, e);
+            const float acc = __uint_as_float(v[e]);
+            o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
+          }
+          if (row < p.S) {
+            if (vec_ok) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (k0 + g * 4 < p.K) {
+                  *reinterpret_cast<float4*>(out_row + k0 + g * 4) =
+                      make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                if (k0 + e < p.K) out_row[k0 + e] = o[e];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[buf]);
+        mbar_arrive(&msum_empty[slot]);
+      }
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ transform: P operand generator
+    const int tt = threadIdx.x - 8 * 32;
+    const int n = tt % BN;       // column of the tile owned by this thread
+    const int grp = tt / BN;     // this thread's group takes k-blocks with i % NGROUPS == grp
+    constexpr int NG = Cfg::NGROUPS;
+    uint32_t it = 0, tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      int r, n0, s0;
+      decode(tile, r, n0, s0);
+      const int kcol = n0 + n;
+      const bool col_ok = kcol < p.K;
+      const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
+      const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + kcol;
+
+      // Column maxima, clamped as the reference does (baselines/lt2exp.py:15-19): an all -inf column
+      // gets -1e38, its exps are exact zeros and the result is -inf, never NaN.
+      const float ma = clamp_stab(col_ok ? column_max(a_col, p.a_s1, p.I) : -INFINITY);
+      const float mb = clamp_stab(col_ok ? column_max(b_col, p.b_s1, p.J) : -INFINITY);
+      const int slot = tcount & 1;
+      if (grp == 0) {
+        if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        msum[slot * BN + n] = ma + mb;
+      }
+
+      for (int jc = 0; ok && jc < JC; ++jc) {
+        // exp(b - mb) for this thread's column and the 32 j of the chunk; zero past J or K.
+        float eb[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int j = jc * BK + x;
+          eb[x] = (col_ok && j < p.J) ? exp_shifted(__ldg(b_col + static_cast<int64_t>(j) * p.b_s1), mb) : 0.f;
+        }
+        // Raw a values of this group's next PF k-blocks.
+        float apf[PF];
+#pragma unroll
+        for (int x = 0; x < PF; ++x) {
+          const int i = grp + x * NG;
+          apf[x] = (col_ok && i < p.I) ? __ldg(a_col + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
+        }
+        for (int ib = 0; ok && ib < p.I; ib += PF * NG) {
+          float acur[PF];
+#pragma unroll
+          for (int x = 0; x < PF; ++x) {
+            acur[x] = apf[x];
+            const int i = ib + PF * NG + grp + x * NG;
+            apf[x] = (col_ok && i < p.I) ? __ldg(a_col + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
+          }
+#pragma unroll
+          for (int x = 0; x < PF; ++x) {
+            const int i = ib + grp + x * NG;
+            if (i >= p.I) break;
+            const uint32_t my_it = it + static_cast<uint32_t>(i);  // k-block index of (jc, i)
+            const int s = my_it % NS;
+            const uint32_t ph = (my_it / NS) & 1;
+            if (!(ok = mbar_wait_warp(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+            const float ea = exp_shifted(acur[x], ma);  // acur = -inf past K: exact zero
+            uint8_t* bh = b_tile(s, 0);
+            uint8_t* bl = b_tile(s, PREC ? 1 : 0);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint32_t off = static_cast<uint32_t>(n) * 128u + ((static_cast<uint32_t>(g) ^ (n & 7u)) << 4);
+              const float p0 = ea * eb[g * 4 + 0], p1 = ea * eb[g * 4 + 1];
+              const float p2 = ea * eb[g * 4 + 2], p3 = ea * eb[g * 4 + 3];
+              if (PREC) {
+                float4 h, l;
+                tf32_split_rn(p0, h.x, l.x);
+                tf32_split_rn(p1, h.y, l.y);
+                tf32_split_rn(p2, h.z, l.z);
+                tf32_split_rn(p3, h.w, l.w);
+                *reinterpret_cast<float4*>(bh + off) = h;
+                *reinterpret_cast<float4*>(bl + off) = l;
+              } else {
+                uint4 u;
+                u.x = tf32_round_bits(p0);
+                u.y = tf32_round_bits(p1);
+                u.z = tf32_round_bits(p2);
+                u.w = tf32_round_bits(p3);
+                *reinterpret_cast<uint4*>(bh + off) = u;
+              }
+            }
+            if (PREC) {
+              // Split the w tiles in place (hi keeps the tf32 bits, lo = w - hi).
+              if (!(ok = mbar_wait_warp(&a_full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+              float4* ah = reinterpret_cast<float4*>(a_tile(s, 0, 0));
+              float4* al = reinterpret_cast<float4*>(a_tile(s, 1, 0));
+              for (int c = n; c < MT * Cfg::A_TILE / 16; c += BN) {
+                const float4 v = ah[c];
+                float4 h, l;
+                tf32_split_trunc(v.x, h.x, l.x);
+                tf32_split_trunc(v.y, h.y, l.y);
+                tf32_split_trunc(v.z, h.z, l.z);
+                tf32_split_trunc(v.w, h.w, l.w);
+                ah[c] = h;
+                al[c] = l;
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&b_full[s]);
+          }
+        }
+        it += static_cast<uint32_t>(p.I);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace tb200

@@ -1,0 +1,261 @@
+// Thin inline-PTX wrappers for the sm_100a features the contraction kernels use:
+// mbarrier (with bounded waits), TMA tiled loads, tcgen05 (TMEM alloc, MMA, commit, ld) and
+// the proxy / tcgen05 fences that order them.
+//
+// Every wait in this file is bounded: a wait that runs past WAIT_LIMIT_CYCLES raises the CTA's
+// abort flag, records an error code in the launch's status word and returns false.  Callers
+// leave their loops on `false`, meet at the CTA's final barrier and free TMEM, so a
+// protocol bug ends as an error code on the host and never as a hung GPU.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb200 {
+
+// ~1.5 s at 1.9 GHz.  Legitimate waits are tens of microseconds.
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;
+
+// Error codes written to the status word (first failure wins).
+enum StatusCode : int {
+  STATUS_OK = 0,
+  STATUS_TIMEOUT_PRODUCER = 101,
+  STATUS_TIMEOUT_TRANSFORM = 102,
+  STATUS_TIMEOUT_MMA = 103,
+  STATUS_TIMEOUT_EPILOGUE = 104,
+  STATUS_TIMEOUT_SETUP = 105,
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ----------------------------------------------------------------------------- mbarrier
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Per-CTA abort state shared by all roles.
+struct AbortCtl {
+  volatile int* flag;   // shared memory, set once any wait gives up
+  int* status;          // global status word of the launch (may be nullptr)
+};
+
+__device__ __forceinline__ void raise_abort(const AbortCtl& ctl, int code) {
+  *ctl.flag = 1;
+  if (ctl.status != nullptr) atomicCAS(ctl.status, 0, code);
+}
+
+// Bounded wait on one phase of an mbarrier.  Returns false if the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*ctl.flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      raise_abort(ctl, code);
+      return false;
+    }
+  }
+}
+
+// Same wait, made warp-uniform: either every lane sees the phase complete or every lane leaves.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code) {
+  const bool ok = mbar_wait(bar, parity, ctl, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// ----------------------------------------------------------------------------- fences
+
+// Generic-proxy shared-memory writes -> visible to the async proxy (TMA, tcgen05.mma operands).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------- TMA (no multicast anywhere)
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+
+// 3-D tiled load global -> this CTA's shared memory; completion counted in bytes on `bar`.
+// x is the innermost coordinate and must keep x * 4 bytes a multiple of 16.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y,
+                                            int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y,
+                                            int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z),
+      "r"(w)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------- TMEM
+
+// Whole-warp collectives.  ncols: power of two in [32, 512].
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// 32 lanes x 32 consecutive columns: lane l of the warp receives columns [c, c+32) of TMEM lane
+// (lane field of taddr) + l.  A warp may only touch the lane quarter 32 * (warp_id % 4).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------- tcgen05.mma (TF32, operands in smem)
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes (32 fp32) wide and
+// stored with the 128-byte swizzle (16-byte chunk index XOR row % 8); 8-row groups are 1024 bytes apart.
+// The tile base must be 1024-byte aligned.  Advancing the contraction index by 8 elements (one
+// MMA) adds 32 bytes, i.e. 2 to the encoded start address.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset: unused for swizzled K-major
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version of this architecture
+  d |= static_cast<uint64_t>(2) << 61;                      // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: D = fp32, A = B = tf32, both K-major, dense, no negate.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// One MMA D[tmem] (+)= A[smem] * B[smem], issued by a single thread.
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive on `bar` once every MMA issued so far by this thread has finished (implies
+// tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// ----------------------------------------------------------------------------- math helpers
+
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float LN2_F = 0.6931471805599453f;
+constexpr float STAB_CLAMP = 1e38f;  // the reference clamps the stabiliser to +-1e38 (baselines/lm2exp.py:12)
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// exp(v - m) with the subtraction done first, as the reference does (baselines/lm2exp.py:13).
+__device__ __forceinline__ float exp_shifted(float v, float m) { return ex2_approx((v - m) * LOG2E_F); }
+
+// Round an fp32 in [0, +inf) to the nearest tf32 (ties away), as raw bits.  The tensor core drops the low
+// 13 mantissa bits of its operands, so adding half a tf32 ulp beforehand turns that truncation into
+// rounding.  Not valid for inf/nan.
+__device__ __forceinline__ uint32_t tf32_round_bits(float x) { return __float_as_uint(x) + 0x1000u; }
+
+// Exact hi/lo split for the 3xTF32 scheme: hi has only tf32 bits set, lo = x - hi is exact in fp32.
+__device__ __forceinline__ void tf32_split_rn(float x, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+  lo = x - hi;
+}
+__device__ __forceinline__ void tf32_split_trunc(float x, float& hi, float& lo) {
+  hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  lo = x - hi;
+}
+
+__device__ __forceinline__ float clamp_stab(float m) { return fminf(fmaxf(m, -STAB_CLAMP), STAB_CLAMP); }
+
+// Byte offset of element (row, col) inside a 128-byte-swizzled K-major tile (rows of 32 fp32).
+__device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t col) {
+  return row * 128u + ((((col >> 2) ^ (row & 7u)) << 4) | ((col & 3u) << 2));
+}
+
+}  // namespace tb200

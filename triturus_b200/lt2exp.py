@@ -1,0 +1,47 @@
+"""lt2exp host wrapper: same signature, checks and result as triturus/lt2exp.py:519-630."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .utils import resolve_precision
+
+_MODES = ("auto", "split", "unsplit")
+
+
+def lt2exp(
+    w: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    mode: str = "auto",
+    precision: str | None = None,
+    variant: int = 0,
+) -> torch.Tensor:
+    """out[r,s,k] = log sum_{i,j} w[r,s,i,j] * exp(a[r,i,k]) * exp(b[r,j,k]) for fp32 CUDA tensors
+    w [R,S,I,J], a [R,I,K], b [R,J,K].
+
+    Assertions and the `mode` check are the reference's (triturus/lt2exp.py:522-541): an unknown mode
+    raises ValueError.  The reference's "split" mode exists to fill the GPU when R*S*K is small by merging
+    partial sums in log space under a spin lock (triturus/lt2exp.py:498-506); this implementation computes
+    every mode with the same deterministic kernel, so the three modes return identical results.
+    """
+    assert len(w.shape) == 4
+    assert len(a.shape) == len(b.shape) == 3
+    assert w.shape[0] == a.shape[0] == b.shape[0]
+    assert w.shape[2] == a.shape[1]
+    assert w.shape[3] == b.shape[1]
+    assert a.shape[2] == b.shape[2]
+    assert w.dtype == a.dtype == b.dtype == torch.float32
+    assert w.device == a.device == b.device
+    if mode not in _MODES:
+        raise ValueError(f"Uknown mode '{mode}' for the l2exp kernel")
+    # The reference flattens the last two dimensions of w with .view (triturus/lt2exp.py:549), which
+    # raises when they are not jointly contiguous; keep that contract.
+    w.view(w.shape[0], w.shape[1], -1)
+    _native._require_cuda(w, a, b)
+    prec = resolve_precision(precision)
+    if w.numel() == 0 or a.numel() == 0 or b.numel() == 0:
+        raise ValueError("lt2exp: empty operands are not supported")
+    return _native.lt2exp_op(w, a, b, prec, int(variant))
