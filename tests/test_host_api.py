@@ -1,0 +1,146 @@
+"""CPU: the C-ABI library loads and exports what include/triturus_b200.h declares; the Python wrappers keep
+the reference's argument checks; nothing here launches a kernel."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import triturus_b200
+from triturus_b200 import _native
+from triturus_b200 import build as tb_build
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "triturus_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(triturus_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    names = _declared_symbols()
+    assert "triturus_b200_lm2exp_f32" in names and "triturus_b200_lt2exp_f32" in names
+    lib = ctypes.CDLL(str(tb_build.LIB_PATH))
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    for n in _native.EXPORTED_SYMBOLS:
+        assert n in names, f"{n} bound in Python but not declared in the header"
+
+
+def test_version_and_strerror():
+    assert _native.LIB.triturus_b200_version() >= 100
+    assert _native.strerror(0) == "ok"
+    assert "align" in _native.strerror(-2)
+    assert "timed out" in _native.strerror(103)
+
+
+def test_workspace_bytes():
+    f = _native.LIB.triturus_b200_lm2exp_workspace_bytes
+    assert f(32, 1024, 1024, 1024) == 32 * 1024 * 4
+    assert f(0, 1, 1, 1) == 0
+
+
+def test_argument_validation_returns_codes_without_a_gpu():
+    """Bad arguments are rejected before any CUDA call, so these run on a CPU-only machine."""
+    lib = _native.LIB
+    s3 = _native._i64([12, 4, 1])
+    null = ctypes.c_void_p(0)
+    fake = ctypes.c_void_p(4096)
+    rc = lib.triturus_b200_lm2exp_f32(null, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -1  # NULL operand
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 0, 4, 4, s3, s3, s3, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -1  # empty dimension
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 7, 0, fake, 1 << 20, null, null)
+    assert rc == -1  # unknown precision
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, 8, null, null)
+    assert rc == -3  # workspace too small
+    bad = _native._i64([12, 4, 2])
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, bad, s3, s3, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -2  # innermost stride must be 1
+    odd = _native._i64([14, 7, 1])
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 2, 2, 4, 4, odd, s3, s3, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -2  # row stride not a multiple of 4 elements
+    s4 = _native._i64([48, 16, 4, 1])
+    rc = lib.triturus_b200_lt2exp_f32(fake, fake, fake, null, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 0, null, null)
+    assert rc == -1
+    rc = lib.triturus_b200_lt2exp_f32(fake, fake, fake, fake, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 5, null, null)
+    assert rc == -1  # unknown variant
+
+
+def test_wrappers_keep_reference_assertions():
+    from triturus.lm2exp import lm2exp
+    from triturus.lt2exp import lt2exp
+
+    with pytest.raises(AssertionError):
+        lm2exp(torch.rand(2, 3), torch.rand(2, 3, 4))
+    with pytest.raises(AssertionError):
+        lm2exp(torch.rand(2, 3, 4), torch.rand(3, 4, 5))
+    with pytest.raises(AssertionError):
+        lm2exp(torch.rand(2, 3, 4), torch.rand(2, 5, 5))
+    with pytest.raises(AssertionError):
+        lm2exp(torch.rand(2, 3, 4).double(), torch.rand(2, 4, 5).double())
+    with pytest.raises(AssertionError):
+        lt2exp(torch.rand(2, 3, 4, 5), torch.rand(2, 4, 6), torch.rand(2, 4, 6))
+    with pytest.raises(AssertionError):
+        lt2exp(torch.rand(2, 3, 4), torch.rand(2, 4, 6), torch.rand(2, 5, 6))
+    with pytest.raises(ValueError):
+        lt2exp(torch.rand(2, 3, 4, 5), torch.rand(2, 4, 6), torch.rand(2, 5, 6), mode="bogus")
+
+
+def test_no_cpu_fallback():
+    """CPU tensors are refused: the product path is the CUDA library only."""
+    with pytest.raises(triturus_b200.NativeLibraryError):
+        triturus_b200.lm2exp(torch.rand(2, 3, 4), torch.rand(2, 4, 5))
+    with pytest.raises(triturus_b200.NativeLibraryError):
+        triturus_b200.lt2exp(torch.rand(2, 3, 4, 5), torch.rand(2, 4, 6), torch.rand(2, 5, 6))
+
+
+def test_precision_flag_mapping():
+    from triturus.utils import is_triturus_tf32_enabled, set_tf32_enabled
+    from triturus_b200.utils import resolve_precision
+
+    assert not is_triturus_tf32_enabled() and resolve_precision(None) == 1
+    set_tf32_enabled(True)
+    assert is_triturus_tf32_enabled() and resolve_precision(None) == 0
+    assert torch.backends.cuda.matmul.allow_tf32
+    set_tf32_enabled(False)
+    assert resolve_precision("tf32") == 0 and resolve_precision("3xtf32") == 1
+    with pytest.raises(ValueError):
+        resolve_precision("fp16")
+
+
+def test_fake_kernels_infer_shapes():
+    a = torch.empty(3, 5, 7, device="meta")
+    b = torch.empty(3, 7, 9, device="meta")
+    assert torch.ops.triturus.lm2exp(a, b, 0, 0).shape == (3, 5, 9)
+    w = torch.empty(3, 4, 5, 7, device="meta")
+    a = torch.empty(3, 5, 9, device="meta")
+    assert torch.ops.triturus.lt2exp(w, a, b, 1, 0).shape == (3, 4, 9)
+
+
+def test_tma_ready_padding_rules():
+    t = torch.rand(2, 3, 50)
+    v = _native._tma_ready(t)
+    assert v.shape == t.shape and v.stride(-1) == 1 and v.stride(1) % 4 == 0 and torch.equal(v, t)
+    t2 = torch.rand(2, 3, 48)
+    assert _native._tma_ready(t2) is t2
+    t3 = torch.rand(2, 48, 3).transpose(1, 2)
+    v3 = _native._tma_ready(t3)
+    assert v3.stride(-1) == 1 and torch.equal(v3, t3)
+
+
+def test_workload_generators_are_seeded_and_shaped():
+    from triturus_b200.workloads import WORKLOADS, make_inputs
+
+    wl = WORKLOADS["cfg2"].with_batch(1)
+    a1, b1 = make_inputs(wl, seed=0)
+    a2, b2 = make_inputs(wl, seed=0)
+    assert torch.equal(a1, a2) and torch.equal(b1, b2)
+    assert a1.shape == (1, 1024, 1024) and b1.shape == (1, 1024, 1024)
+    assert torch.isinf(b1).float().mean() > 0.005
+    assert WORKLOADS["cfg2"].flops == 2.0 * 32 * 1024**3
+    assert WORKLOADS["cfg5"].bytes == 4.0 * 64 * (256 * 128 * 128 + 2 * 128 * 4096 + 256 * 4096)

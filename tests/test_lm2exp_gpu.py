@@ -1,0 +1,176 @@
+"""GPU parity tests for lm2exp: the CUDA path (through the C ABI) against the golden fixtures produced by
+the reference's baseline, against the float64 oracle, and through size-independent properties at the full
+benchmark sizes.  Tolerances (absolute, log space, vs float64): 2e-3 for TF32, 1e-4 for 3xTF32; -inf
+positions must match exactly and no NaN may appear."""
+
+import pytest
+import torch
+
+from conftest import ATOL, LM_GOLDEN, load_golden
+from oracle import logspace_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+PRECISIONS = ["tf32", "3xtf32"]
+VARIANTS = [0, 1281, 1282, 2561, 2562]
+
+
+def _run(a, b, **kw):
+    import triturus_b200 as tb
+
+    out = tb.lm2exp(a.cuda(), b.cuda(), **kw)
+    tb.check_status()
+    return out.cpu()
+
+
+def _assert_close(got, a, b, precision, want64=None):
+    want64 = orc.lm2exp_fp64(a, b) if want64 is None else want64
+    res = orc.compare_logspace(got, want64, ATOL[precision])
+    assert res["ok"], res
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("name", LM_GOLDEN)
+def test_golden(name, precision):
+    g = load_golden(name)
+    got = _run(g["a"], g["b"], precision=precision)
+    # against the reference baseline's stored output (fp32, itself ~1e-5 from exact)
+    res = orc.compare_logspace(got, g["out"], ATOL[precision] + 2e-5)
+    assert res["ok"], res
+    _assert_close(got, g["a"], g["b"], precision)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_variants_on_ragged_shape(precision, variant):
+    g = torch.Generator().manual_seed(7)
+    a = torch.rand(5, 300, 171, generator=g)
+    b = torch.randn(5, 171, 530, generator=g) * 5.0 + 100.0 * torch.randn(5, 1, 530, generator=g)
+    got = _run(a, b, precision=precision, variant=variant)
+    _assert_close(got, a, b, precision)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (1, 1, 33, 5), (2, 129, 31, 3), (3, 7, 64, 257), (1, 260, 5, 1030),
+                                   (2, 128, 32, 128), (4, 256, 96, 256)])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_edge_shapes(shape, precision):
+    R, I, J, K = shape
+    g = torch.Generator().manual_seed(R * 1000 + I + J + K)
+    a = torch.rand(R, I, J, generator=g) + 0.01
+    b = torch.randn(R, J, K, generator=g) * 3.0
+    got = _run(a, b, precision=precision)
+    assert got.shape == (R, I, K) and got.is_contiguous()
+    _assert_close(got, a, b, precision)
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_neginf_columns_and_entries(precision):
+    g = torch.Generator().manual_seed(3)
+    R, I, J, K = 3, 140, 70, 300
+    a = torch.rand(R, I, J, generator=g)
+    b = torch.randn(R, J, K, generator=g) * 40.0
+    b[0, :, 17] = float("-inf")         # whole column
+    b[1, :, 0] = float("-inf")
+    b[2, :, K - 1] = float("-inf")
+    b[torch.rand(R, J, K, generator=g) < 0.05] = float("-inf")  # isolated entries
+    b[1, : J - 1, 40] = float("-inf")   # a column with a single finite entry
+    got = _run(a, b, precision=precision)
+    assert not torch.isnan(got).any()
+    want = orc.lm2exp_fp64(a, b)
+    assert torch.all(got[0, :, 17] == float("-inf"))
+    assert torch.equal(got == float("-inf"), want == float("-inf"))
+    _assert_close(got, a, b, precision, want)
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_huge_offsets(precision):
+    g = torch.Generator().manual_seed(5)
+    a = torch.rand(2, 64, 128, generator=g)
+    b = torch.randn(2, 128, 96, generator=g) * 10.0 + (400.0 * torch.rand(2, 1, 96, generator=g) - 200.0) * 100.0
+    got = _run(a, b, precision=precision)
+    want = orc.lm2exp_fp64(a, b)
+    # values reach ~2e4, where one fp32 ulp is ~2e-3: compare relatively
+    assert torch.allclose(got.double(), want, rtol=3e-7 if precision == "3xtf32" else 1e-6, atol=ATOL[precision])
+
+
+def test_noncontiguous_inputs_and_inputs_untouched():
+    g = torch.Generator().manual_seed(11)
+    a_full = torch.rand(4, 100, 2 * 52, generator=g).cuda()
+    b_t = torch.randn(4, 88, 52, generator=g).cuda()
+    a = a_full[:, :, ::2]              # innermost stride 2 -> copy path
+    b = b_t.transpose(1, 2)            # [4, 52, 88] with innermost stride 52 -> copy path
+    a_before, b_before = a.clone(), b.clone()
+    import triturus_b200 as tb
+
+    got = tb.lm2exp(a, b, precision="3xtf32")
+    tb.check_status()
+    assert torch.equal(a, a_before) and torch.equal(b, b_before)
+    _assert_close(got.cpu(), a.cpu().contiguous(), b.cpu().contiguous(), "3xtf32")
+    # strided batch / row views that already satisfy the TMA rules take the no-copy path
+    big_a = torch.rand(6, 128, 64, generator=g).cuda()
+    big_b = torch.randn(6, 64, 256, generator=g).cuda()
+    got2 = tb.lm2exp(big_a[::2, 16:80], big_b[::2, :, 64:192], precision="3xtf32")
+    tb.check_status()
+    _assert_close(got2.cpu(), big_a[::2, 16:80].cpu().contiguous(), big_b[::2, :, 64:192].cpu().contiguous(), "3xtf32")
+
+
+def test_global_flag_selects_precision():
+    from triturus.lm2exp import lm2exp
+    from triturus.utils import set_tf32_enabled
+
+    g = torch.Generator().manual_seed(13)
+    a = torch.rand(2, 130, 100, generator=g).cuda()
+    b = torch.randn(2, 100, 90, generator=g).cuda()
+    set_tf32_enabled(False)
+    hi = lm2exp(a, b)
+    set_tf32_enabled(True)
+    lo = lm2exp(a, b)
+    set_tf32_enabled(False)
+    want = orc.lm2exp_fp64(a.cpu(), b.cpu())
+    e_hi = (hi.cpu().double() - want).abs().max().item()
+    e_lo = (lo.cpu().double() - want).abs().max().item()
+    assert e_hi <= 1e-4 and e_lo <= 2e-3 and e_hi < e_lo
+
+
+def test_torch_op_is_registered_and_deterministic():
+    g = torch.Generator().manual_seed(17)
+    a = torch.rand(3, 200, 64, generator=g).cuda()
+    b = torch.randn(3, 64, 300, generator=g).cuda()
+    x = torch.ops.triturus.lm2exp(a, b, 0, 0)
+    y = torch.ops.triturus.lm2exp(a, b, 0, 0)
+    assert torch.equal(x, y)
+    # batch permutation equivariance, bit for bit: the result of a batch entry does not depend on
+    # which CTA or tile slot computed it
+    perm = torch.tensor([2, 0, 1]).cuda()
+    z = torch.ops.triturus.lm2exp(a[perm].contiguous(), b[perm].contiguous(), 0, 0)
+    assert torch.equal(z, x[perm])
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3"])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_full_size_configs(name, precision):
+    """The benchmark configurations at full size: float64 oracle on a batch subset, plus shift and scale
+    identities on the whole result."""
+    import triturus_b200 as tb
+    from triturus_b200.workloads import WORKLOADS, make_inputs
+
+    wl = WORKLOADS[name]
+    a, b = make_inputs(wl, seed=0)
+    ad, bd = a.cuda(), b.cuda()
+    out = tb.lm2exp(ad, bd, precision=precision)
+    tb.check_status()
+    assert not torch.isnan(out).any()
+    rs = sorted({0, wl.dims["R"] // 2, wl.dims["R"] - 1})
+    want = orc.lm2exp_fp64(a[rs], b[rs])
+    res = orc.compare_logspace(out[rs].cpu(), want, ATOL[precision])
+    assert res["ok"], res
+    # shift identity: adding c[r,k] to every b[r,:,k] adds c[r,k] to the result
+    shift = torch.linspace(-3.0, 5.0, wl.dims["K"]).view(1, 1, -1).cuda()
+    out_s = tb.lm2exp(ad, bd + shift, precision=precision)
+    fin = torch.isfinite(out)
+    assert torch.equal(torch.isfinite(out_s), fin)
+    assert (out_s - shift - out)[fin].abs().max().item() <= 2 * ATOL[precision]
+    # scale identity: multiplying a by 2^k adds k*log(2) exactly in exact arithmetic
+    out_2 = tb.lm2exp(ad * 4.0, bd, precision=precision)
+    assert (out_2 - out - 2.0 * 0.6931471805599453)[fin].abs().max().item() <= 1e-4
+    tb.check_status()

@@ -1,0 +1,156 @@
+"""GPU parity tests for lt2exp (through the C ABI): golden fixtures from the reference's baselines, the
+float64 oracle, edge cases and full-size properties.  Tolerances as in test_lm2exp_gpu.py."""
+
+import pytest
+import torch
+
+from conftest import ATOL, LT_GOLDEN, load_golden
+from oracle import logspace_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+PRECISIONS = ["tf32", "3xtf32"]
+VARIANTS = [0, 1281, 1282, 2561, 2562]
+
+
+def _run(w, a, b, **kw):
+    import triturus_b200 as tb
+
+    out = tb.lt2exp(w.cuda(), a.cuda(), b.cuda(), **kw)
+    tb.check_status()
+    return out.cpu()
+
+
+def _assert_close(got, w, a, b, precision, want64=None):
+    want64 = orc.lt2exp_fp64(w, a, b, chunk=2) if want64 is None else want64
+    res = orc.compare_logspace(got, want64, ATOL[precision])
+    assert res["ok"], res
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("name", LT_GOLDEN)
+def test_golden(name, precision):
+    g = load_golden(name)
+    got = _run(g["w"], g["a"], g["b"], precision=precision)
+    res = orc.compare_logspace(got, g["out"], ATOL[precision] + 2e-5)
+    assert res["ok"], res
+    _assert_close(got, g["w"], g["a"], g["b"], precision)
+
+
+@pytest.mark.parametrize("mode", ["auto", "split", "unsplit"])
+def test_modes_agree(mode):
+    g = load_golden("lt_reftest")
+    got = _run(g["w"], g["a"], g["b"], mode=mode, precision="3xtf32")
+    base = _run(g["w"], g["a"], g["b"], mode="unsplit", precision="3xtf32")
+    assert torch.equal(got, base)
+
+
+def test_unknown_mode_raises():
+    import triturus_b200 as tb
+
+    g = load_golden("lt_neginf")
+    with pytest.raises(ValueError):
+        tb.lt2exp(g["w"].cuda(), g["a"].cuda(), g["b"].cuda(), mode="fast")
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_variants_on_ragged_shape(precision, variant):
+    g = torch.Generator().manual_seed(9)
+    w = torch.rand(3, 270, 13, 37, generator=g)
+    a = torch.randn(3, 13, 300, generator=g) * 4.0 + 50.0 * torch.randn(3, 1, 300, generator=g)
+    b = torch.randn(3, 37, 300, generator=g) * 4.0
+    got = _run(w, a, b, precision=precision, variant=variant)
+    _assert_close(got, w, a, b, precision)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1), (1, 3, 1, 33, 5), (2, 129, 5, 1, 3), (2, 7, 9, 64, 257),
+                                   (1, 130, 20, 31, 70), (2, 128, 4, 32, 128), (1, 64, 17, 96, 258)])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_edge_shapes(shape, precision):
+    R, S, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    w = torch.rand(R, S, I, J, generator=g) + 0.01
+    a = torch.randn(R, I, K, generator=g) * 3.0
+    b = torch.randn(R, J, K, generator=g) * 3.0
+    got = _run(w, a, b, precision=precision)
+    assert got.shape == (R, S, K) and got.is_contiguous()
+    _assert_close(got, w, a, b, precision)
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_neginf_columns_and_entries(precision):
+    g = torch.Generator().manual_seed(4)
+    R, S, I, J, K = 2, 140, 12, 40, 200
+    w = torch.rand(R, S, I, J, generator=g)
+    a = torch.randn(R, I, K, generator=g) * 30.0
+    b = torch.randn(R, J, K, generator=g) * 30.0
+    a[0, :, 7] = float("-inf")
+    b[1, :, 199] = float("-inf")
+    a[1, :, 50] = float("-inf")
+    b[1, :, 50] = float("-inf")
+    a[torch.rand(R, I, K, generator=g) < 0.05] = float("-inf")
+    b[torch.rand(R, J, K, generator=g) < 0.05] = float("-inf")
+    got = _run(w, a, b, precision=precision)
+    assert not torch.isnan(got).any()
+    want = orc.lt2exp_fp64(w, a, b)
+    assert torch.all(got[0, :, 7] == float("-inf")) and torch.all(got[1, :, 50] == float("-inf"))
+    assert torch.equal(got == float("-inf"), want == float("-inf"))
+    _assert_close(got, w, a, b, precision, want)
+
+
+def test_noncontiguous_a_b_and_w_view_contract():
+    import triturus_b200 as tb
+
+    g = torch.Generator().manual_seed(21)
+    w = torch.rand(2, 40, 6, 20, generator=g).cuda()
+    a_t = torch.randn(2, 90, 6, generator=g).cuda()
+    b_big = torch.randn(2, 20, 180, generator=g).cuda()
+    a = a_t.transpose(1, 2)        # [2, 6, 90], innermost stride 6
+    b = b_big[:, :, ::2]           # [2, 20, 90], innermost stride 2
+    got = tb.lt2exp(w, a, b, precision="3xtf32")
+    tb.check_status()
+    _assert_close(got.cpu(), w.cpu(), a.cpu().contiguous(), b.cpu().contiguous(), "3xtf32")
+    # like the reference (triturus/lt2exp.py:549), w must allow .view(R, S, -1)
+    w_bad = torch.rand(2, 40, 20, 6, generator=g).cuda().transpose(2, 3)  # [2, 40, 6, 20], not viewable
+    with pytest.raises(RuntimeError):
+        tb.lt2exp(w_bad, a, b)
+
+
+def test_batch_permutation_is_bit_exact():
+    g = torch.Generator().manual_seed(23)
+    w = torch.rand(3, 150, 8, 40, generator=g).cuda()
+    a = torch.randn(3, 8, 260, generator=g).cuda()
+    b = torch.randn(3, 40, 260, generator=g).cuda()
+    x = torch.ops.triturus.lt2exp(w, a, b, 0, 0)
+    perm = torch.tensor([1, 2, 0]).cuda()
+    z = torch.ops.triturus.lt2exp(w[perm].contiguous(), a[perm].contiguous(), b[perm].contiguous(), 0, 0)
+    assert torch.equal(z, x[perm])
+
+
+@pytest.mark.parametrize("name,batch", [("cfg4", 16), ("cfg5", 4)])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_full_size_configs(name, batch, precision):
+    """cfg4 at full size; cfg5 with its full S, I, J, K and four batch entries (one entry of cfg5 is
+    17 G multiply-adds for the float64 oracle).  Oracle on a batch subset plus the shift identity."""
+    import triturus_b200 as tb
+    from triturus_b200.workloads import WORKLOADS, make_inputs
+
+    wl = WORKLOADS[name].with_batch(batch)
+    w, a, b = make_inputs(wl, seed=0)
+    wd, ad, bd = w.cuda(), a.cuda(), b.cuda()
+    out = tb.lt2exp(wd, ad, bd, precision=precision)
+    tb.check_status()
+    assert not torch.isnan(out).any()
+    rs = [0, batch - 1] if name == "cfg4" else [batch - 1]
+    want = orc.lt2exp_fp64(w[rs], a[rs], b[rs])
+    res = orc.compare_logspace(out[rs].cpu(), want, ATOL[precision])
+    assert res["ok"], res
+    K = wl.dims["K"]
+    sa = torch.linspace(-2.0, 3.0, K).view(1, 1, -1).cuda()
+    sb = torch.linspace(4.0, -1.0, K).view(1, 1, -1).cuda()
+    out_s = tb.lt2exp(wd, ad + sa, bd + sb, precision=precision)
+    fin = torch.isfinite(out)
+    assert torch.equal(torch.isfinite(out_s), fin)
+    assert (out_s - sa - sb - out)[fin].abs().max().item() <= 2 * ATOL[precision]
+    tb.check_status()
