@@ -239,8 +239,16 @@ def main() -> None:
     for _ in range(warmup):
         out = step(*inputs)
     tb.check_status()
+    # The timed region can be a few milliseconds, shorter than one nvidia-smi sampling period, so the same
+    # step keeps the GPU loaded (untimed) until the sampler has delivered samples before the timed region
+    # and for a short while after it; the reported clock is the median of the samples under that load.
     sampler = ClockSampler(local_rank)
     sampler.start()
+    lead_in_deadline = time.perf_counter() + 4.0
+    while len(sampler.lines) < 3 and time.perf_counter() < lead_in_deadline:
+        for _ in range(8):
+            out = step(*inputs)
+        torch.cuda.synchronize()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     barrier()
     t_wall0 = time.perf_counter()
@@ -250,7 +258,14 @@ def main() -> None:
         e1.record()
     barrier()
     t_wall = time.perf_counter() - t_wall0
+    n_before = len(sampler.lines)
+    lead_out_deadline = time.perf_counter() + 1.5
+    while len(sampler.lines) < n_before + 3 and time.perf_counter() < lead_out_deadline:
+        for _ in range(8):
+            out = step(*inputs)
+        torch.cuda.synchronize()
     clocks = sampler.stop()
+    clocks["note"] = "sampled every 200 ms while the timed step ran back to back before, during and after the timed region"
     tb.check_status()
     per_step_ms = [e0.elapsed_time(e1) for e0, e1 in evs]
     total_ms = evs[0][0].elapsed_time(evs[-1][1])
