@@ -32,6 +32,7 @@ extern "C" {
 #define TRITURUS_B200_ETENSORMAP (-4)  /* the driver rejected a tensor map */
 #define TRITURUS_B200_ELAUNCH (-5)     /* kernel launch or attribute call failed */
 #define TRITURUS_B200_EDRIVER (-6)     /* driver entry point unavailable */
+#define TRITURUS_B200_ESTATICLIMIT (-7) /* problem exceeds the built-in scratch of the *_static entry point */
 
 #define TRITURUS_B200_PRECISION_TF32 0   /* one tf32 MMA pass; triturus.utils.set_tf32_enabled(True) */
 #define TRITURUS_B200_PRECISION_3XTF32 1 /* hi/lo split, ~fp32 accuracy; set_tf32_enabled(False) */
@@ -81,6 +82,31 @@ int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, flo
  */
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
                              void* stream);
+
+/*
+ * lm2exp for callers that cannot allocate device memory.  (No counterpart in the reference: its wrapper
+ * allocates freely through torch.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- inside an arena or memory pool that already
+ * owns the GPU's memory, in latency-critical loops where an allocation would synchronise the device, or in
+ * plugin hosts that pass in only the input and output buffers.  Same arguments and results as
+ * triturus_b200_lm2exp_f32, minus the workspace: the [R,K] stabiliser scratch is a fixed 4 MiB array inside
+ * the library image (reserved on every GPU that loads the library, until the process exits).
+ *
+ *   Limit:  R * K <= triturus_b200_lm2exp_static_max_columns() (1,048,576); larger problems return
+ *           TRITURUS_B200_ESTATICLIMIT and launch nothing.
+ *   Set-up: the first call on each device looks up the array's device address (that device must be
+ *           current); make that first call before starting any stream capture.
+ *   Sharing: all calls on a device use the same array.  Each call rewrites every element it later reads, so
+ *           stale contents never matter, but two calls whose kernels can overlap on the GPU (different
+ *           streams, no dependency) race on it; keep such calls ordered or use the workspace entry point.
+ *   The function calls no cudaMalloc, cudaFree or any other allocating routine.
+ */
+size_t triturus_b200_lm2exp_static_max_columns(void);
+int triturus_b200_lm2exp_f32_static(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J,
+                                    int64_t K, const int64_t a_strides[3], const int64_t b_strides[3],
+                                    const int64_t out_strides[3], int precision, int variant, int32_t* status_dev,
+                                    void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,6 +23,8 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lm2exp_f32",
     "triturus_b200_lt2exp_f32",
     "triturus_b200_colmax_f32",
+    "triturus_b200_lm2exp_static_max_columns",
+    "triturus_b200_lm2exp_f32_static",
 )
 
 
@@ -30,7 +32,7 @@ class NativeLibraryError(RuntimeError):
     """The shared library is missing, cannot be loaded, or returned an error code."""
 
 
-def _load() -> ctypes.CDLL:
+def _open() -> ctypes.CDLL:
     path = _build.LIB_PATH
     if not path.exists():
         # First use in a fresh checkout: build in-tree.  A failure here is fatal by design.
@@ -41,10 +43,27 @@ def _load() -> ctypes.CDLL:
                 f"{path} is missing and could not be built ({exc}); run `python -m triturus_b200.build`"
             ) from exc
     try:
-        lib = ctypes.CDLL(os.fspath(path))
+        return ctypes.CDLL(os.fspath(path))
     except OSError as exc:
         raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
 
+
+def _load() -> ctypes.CDLL:
+    lib = _open()
+    try:
+        return _bind(lib)
+    except AttributeError:
+        # The library on disk predates a symbol this module binds (sources were updated): unload it,
+        # rebuild once and load the new file.
+        import _ctypes
+
+        _ctypes.dlclose(lib._handle)
+        del lib
+        _build.build(force=True)
+        return _bind(_open())
+
+
+def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     i64p = POINTER(c_int64)
     lib.triturus_b200_version.restype = c_int
     lib.triturus_b200_version.argtypes = []
@@ -61,6 +80,13 @@ def _load() -> ctypes.CDLL:
     lib.triturus_b200_lt2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
         i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_lm2exp_static_max_columns.restype = c_size_t
+    lib.triturus_b200_lm2exp_static_max_columns.argtypes = []
+    lib.triturus_b200_lm2exp_f32_static.restype = c_int
+    lib.triturus_b200_lm2exp_f32_static.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
+        c_int, c_int, c_void_p, c_void_p,
     ]  # fmt: skip
     lib.triturus_b200_colmax_f32.restype = c_int
     lib.triturus_b200_colmax_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, i64p, c_void_p]

@@ -202,6 +202,7 @@ const char* triturus_b200_strerror(int code) {
     case TRITURUS_B200_ETENSORMAP: return "tensor map rejected by the driver";
     case TRITURUS_B200_ELAUNCH: return "kernel launch failed";
     case TRITURUS_B200_EDRIVER: return "cuTensorMapEncodeTiled unavailable";
+    case TRITURUS_B200_ESTATICLIMIT: return "R * K exceeds the built-in scratch of the static entry point";
     case STATUS_TIMEOUT_PRODUCER: return "device: TMA producer wait timed out";
     case STATUS_TIMEOUT_TRANSFORM: return "device: transform warp wait timed out";
     case STATUS_TIMEOUT_MMA: return "device: MMA issuer wait timed out";
@@ -411,4 +412,62 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
   }
   if (bn == 256) return mt == 2 ? launch_lt2exp<LtT_256_2>(tw, p, st) : launch_lt2exp<LtT_256_1>(tw, p, st);
   return mt == 2 ? launch_lt2exp<LtT_128_2>(tw, p, st) : launch_lt2exp<LtT_128_1>(tw, p, st);
+}
+
+// ----------------------------------------------------------------------------- lm2exp without caller scratch
+//
+// Some callers of this library are not allowed to allocate device memory at the point where they call
+// it: code running inside a memory-pool or arena that owns all of HBM, real-time loops that forbid
+// cudaMalloc because it synchronises the device, and plugin hosts that hand out only input and output
+// buffers.  For them the stabiliser scratch lives in the library image itself.
+//
+// The array below is device memory reserved at module load on every GPU that loads this library
+// (4 MiB per GPU, held until the process exits).  Its name is only meaningful to device code; host code
+// must not pass it to a kernel as if it were a pointer.  The host obtains the real device address once
+// per device with cudaGetSymbolAddress and passes that.
+
+#define TRITURUS_B200_STATIC_STAB_FLOATS (1 << 20)
+
+static __device__ __align__(256) float g_static_stab[TRITURUS_B200_STATIC_STAB_FLOATS];
+
+namespace tb200 {
+
+// Device address of g_static_stab on the current device, resolved on first use per device.
+static int static_stab_address(float** out) {
+  static float* addr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_stab) != cudaSuccess || p == nullptr) return TRITURUS_B200_ELAUNCH;
+    addr[dev] = static_cast<float*>(p);
+  }
+  *out = addr[dev];
+  return TRITURUS_B200_OK;
+}
+
+}  // namespace tb200
+
+extern "C" size_t triturus_b200_lm2exp_static_max_columns(void) { return TRITURUS_B200_STATIC_STAB_FLOATS; }
+
+extern "C" int triturus_b200_lm2exp_f32_static(const float* a, const float* b, float* out, int64_t R, int64_t I,
+                                               int64_t J, int64_t K, const int64_t a_strides[3],
+                                               const int64_t b_strides[3], const int64_t out_strides[3],
+                                               int precision, int variant, int32_t* status_dev, void* stream) {
+  if (R <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  // R * K stabiliser values must fit the built-in array; larger problems need the entry point that takes
+  // a caller workspace.
+  if (R > TRITURUS_B200_STATIC_STAB_FLOATS || K > TRITURUS_B200_STATIC_STAB_FLOATS ||
+      R * K > TRITURUS_B200_STATIC_STAB_FLOATS)
+    return TRITURUS_B200_ESTATICLIMIT;
+  float* scratch = nullptr;
+  const int rc = tb200::static_stab_address(&scratch);
+  if (rc != TRITURUS_B200_OK) return rc;
+  // Every element the contraction kernel reads is overwritten by the stabiliser pre-pass of the same
+  // call, so nothing left behind by an earlier call is ever observed and nothing needs clearing.
+  return triturus_b200_lm2exp_f32(a, b, out, R, I, J, K, a_strides, b_strides, out_strides, precision, variant,
+                                  scratch, static_cast<size_t>(TRITURUS_B200_STATIC_STAB_FLOATS) * sizeof(float),
+                                  status_dev, stream);
 }
