@@ -200,6 +200,9 @@ def main() -> None:
     ap.add_argument("--precision", choices=["tf32", "3xtf32"], default="tf32")
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-mode", action="store_true",
+                    help="only W warm-up and K timed steps: no clock sampling, end-to-end leg or CPU baseline "
+                         "(for runs under a profiler, whose printed numbers are never bench values)")
     ap.add_argument("--gather", action="store_true", help="also time an all-gather of the output shards (reported separately)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -243,8 +246,9 @@ def main() -> None:
     # step keeps the GPU loaded (untimed) until the sampler has delivered samples before the timed region
     # and for a short while after it; the reported clock is the median of the samples under that load.
     sampler = ClockSampler(local_rank)
-    sampler.start()
-    lead_in_deadline = time.perf_counter() + 4.0
+    if not args.profile_mode:
+        sampler.start()
+    lead_in_deadline = time.perf_counter() + (0.0 if args.profile_mode else 4.0)
     while len(sampler.lines) < 3 and time.perf_counter() < lead_in_deadline:
         for _ in range(8):
             out = step(*inputs)
@@ -259,7 +263,7 @@ def main() -> None:
     barrier()
     t_wall = time.perf_counter() - t_wall0
     n_before = len(sampler.lines)
-    lead_out_deadline = time.perf_counter() + 1.5
+    lead_out_deadline = time.perf_counter() + (0.0 if args.profile_mode else 1.5)
     while len(sampler.lines) < n_before + 3 and time.perf_counter() < lead_out_deadline:
         for _ in range(8):
             out = step(*inputs)
@@ -275,6 +279,15 @@ def main() -> None:
     total_ms, launch_ms = float(t[0]), float(t[1])
     ms_per_step = total_ms / steps
     value = world * wl.flops / (ms_per_step * 1e-3) / 1e12
+
+    if args.profile_mode:
+        if rank == 0:
+            print(json.dumps({"profile_mode": True, "workload": wl.name, "ms_per_step": ms_per_step,
+                              "note": "not a bench value"}), flush=True)  # fmt: skip
+        if distributed:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---------------------------------------------------------------- end to end from pinned host memory
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
