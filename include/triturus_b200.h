@@ -50,9 +50,11 @@ const char* triturus_b200_strerror(int code);
  * baselines/lm2exp.py:4-14.
  *   a [R,I,J], b [R,J,K], out [R,I,K]; *_strides = element strides of the three dimensions.
  *   precision: TRITURUS_B200_PRECISION_*.
- *   variant:   0 = choose the tile shape from the problem size; otherwise BN * 10 + MT with
- *              BN in {128, 256} output columns and MT in {1, 2} 128-row blocks per CTA tile
- *              (the counterpart of the reference's autotune table, triturus/lm2exp.py:7-58).
+ *   variant:   0 = choose everything from the problem size; otherwise STAB * 100000 + BN * 10 + MT with
+ *              BN in {128, 256} output columns and MT in {1, 2} 128-row blocks per CTA tile (BN * 10 + MT
+ *              may be 0 = automatic) and STAB selecting where the stabiliser is computed: 0 = automatic,
+ *              1 = pre-pass launch writing the workspace, 2 = max pass fused into the contraction kernel.
+ *              (The counterpart of the reference's autotune table, triturus/lm2exp.py:7-58.)
  *   workspace: at least triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned; holds the
  *              [R,K] stabiliser.
  */

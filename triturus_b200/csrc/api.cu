@@ -162,13 +162,13 @@ static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expPar
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
-//                          BN   MT PREC NS NR NTW
-using LmT_128_1 = Lm2expCfg<128, 1, 0, 4, 3, 8>;
-using LmT_128_2 = Lm2expCfg<128, 2, 0, 3, 3, 8>;
-using LmT_256_1 = Lm2expCfg<256, 1, 0, 3, 2, 8>;
-using LmT_256_2 = Lm2expCfg<256, 2, 0, 2, 2, 8>;
-using LmX_128_1 = Lm2expCfg<128, 1, 1, 2, 2, 8>;
-using LmX_128_2 = Lm2expCfg<128, 2, 1, 2, 2, 8>;
+//                          BN   MT PREC NS
+using LmT_128_1 = Lm2expCfg<128, 1, 0, 6>;
+using LmT_128_2 = Lm2expCfg<128, 2, 0, 4>;
+using LmT_256_1 = Lm2expCfg<256, 1, 0, 4>;
+using LmT_256_2 = Lm2expCfg<256, 2, 0, 3>;
+using LmX_128_1 = Lm2expCfg<128, 1, 1, 3>;
+using LmX_128_2 = Lm2expCfg<128, 2, 1, 2>;
 
 static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt) {
   return R * ((rows + 128 * mt - 1) / (128 * mt)) * ((cols + bn - 1) / bn);
@@ -262,16 +262,26 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
   if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
 
-  if (variant == 0) variant = auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
-  const int bn = variant / 10, mt = variant % 10;
+  if (variant < 0) return TRITURUS_B200_EINVAL;
+  const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
+  int tile_variant = variant % 100000;
+  if (stab_mode > 2) return TRITURUS_B200_EINVAL;
+  if (tile_variant == 0) tile_variant = auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  int bn = tile_variant / 10;
+  const int mt = tile_variant % 10;
   if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
-  const int bn_eff = (precision == TRITURUS_B200_PRECISION_3XTF32) ? 128 : bn;
+  if (precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // the hi/lo copies leave room for 128 columns
+  // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.
+  const bool fused = stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* m_ws = static_cast<float*>(workspace);
-  const int64_t bstr[3] = {bs0, bs1, 1};
-  int rc = triturus_b200_colmax_f32(b, m_ws, R, J, K, bstr, stream);
-  if (rc != TRITURUS_B200_OK) return rc;
+  int rc = TRITURUS_B200_OK;
+  if (!fused) {
+    const int64_t bstr[3] = {bs0, bs1, 1};
+    rc = triturus_b200_colmax_f32(b, m_ws, R, J, K, bstr, stream);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
 
   CUtensorMap ta, tb;
   {
@@ -284,8 +294,8 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   {
     const int64_t dims[3] = {K, J, R};
     const int64_t strides[3] = {1, bs1, bs0};
-    const uint32_t box[3] = {static_cast<uint32_t>(bn_eff), 32, 1};
-    rc = make_tmap(&tb, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tmap(&tb, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc != TRITURUS_B200_OK) return rc;
   }
 
@@ -299,6 +309,7 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   p.J = static_cast<int>(J);
   p.K = static_cast<int>(K);
   p.tiles_m = p.tiles_n = p.num_tiles = 0;
+  p.fused_max = fused ? 1 : 0;
   p.status = status_dev;
 
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {

@@ -1,20 +1,29 @@
 // lm2exp:  out[r,i,k] = m[r,k] + log( sum_j a[r,i,j] * exp(b[r,j,k] - m[r,k]) ),  m = clamp(max_j b, +-1e38)
 //
 // Replaces the reference's Triton kernel _ker_lm2exp (triturus/lm2exp.py:63-164) with one persistent,
-// warp-specialised sm_100a kernel.  As a GEMM: D[M = i, N = k] = A[M, Kc = j] * B[Kc, N].
+// warp-specialised sm_100a kernel.  As a GEMM: D[M = i, N = k] = A[M, Kc = j] * E[Kc, N], E = exp(b - m).
 //
-//   warp 0      TMA producer: a-tiles (128 x 32 fp32, K-major, 128B swizzle) into the operand ring and raw
-//               b-tiles (32 j-rows x BN k-columns, dense) into the raw ring.
+// b is N-major in memory (k contiguous), so E is used as an MN-major tensor-core operand: TMA drops each
+// 32 j-rows x 32 k-columns box of b (128-byte rows, 128-byte swizzle with 32-byte base, the one swizzled
+// layout tf32 MN-major operands may use) straight into the operand stage and the
+// transform warps replace it IN PLACE by tf32-rounded exp(b - m): one 16-byte shared-memory load, four ex2,
+// one 16-byte store per thread and step, no second buffer and no transposition.
+//
+//   warp 0      TMA producer: per k-block MT a-tiles (128 x 32 fp32, K-major, 128B swizzle) and BN/32 b-boxes.
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.kind::tf32 (M = 128, N = BN, K = 8) and commits.
-//   warps 4-7   epilogue: tcgen05.ld the fp32 accumulator, out = m + log(acc), 128-bit stores.
-//   warps 8+    transform: raw b -> exp(b - m) in registers -> tf32-rounded K-major swizzled B operand.
+//   warps 4-7   epilogue: tcgen05.ld, out = m + log(acc), transposed through shared memory so that every
+//               128-bit store instruction writes four full 128-byte row segments.
+//   warps 8-15  transform.  Warp w owns the 32-column group w % (BN/32); lane = 8 * row_slot + 16-byte chunk.
 //
-// One CTA tile is (MT * 128) rows x BN columns; the MT row blocks share each generated B operand, so one
-// exp feeds MT * 128 MACs.  Accumulators live in TMEM (MT * BN columns per buffer, double-buffered when
-// 2 * MT * BN <= 512) so the epilogue of one tile overlaps the main loop of the next.
+// Stabiliser.  Either m comes from a pre-pass through the caller's workspace, or (fused_max) every tile
+// starts with a max pass: the same b boxes stream through the ring once more, the transform warps keep a
+// running maximum per column and fold the four row slots of a warp with shuffles.  The fused form reads b
+// from HBM once and again from L2; it is chosen when each column slab of b is used by a single row tile.
 //
+// One CTA tile is (MT * 128) rows x BN columns; the MT row blocks share each generated operand.
+// Accumulators live in TMEM (MT * BN columns per buffer, double-buffered when 2 * MT * BN <= 512).
 // PREC = 1 selects the 3xTF32 split: a = a_hi + a_lo, e = e_hi + e_lo and
-// acc += a_hi*e_lo + a_lo*e_hi + a_hi*e_hi, which restores ~fp32 accuracy at a third of the MMA rate.
+// acc += a_hi*e_lo + a_lo*e_hi + a_hi*e_hi.
 #pragma once
 
 #include "ptx.cuh"
@@ -22,34 +31,40 @@
 namespace tb200 {
 
 struct Lm2expParams {
-  const float* m_ws;   // [R, K] clamped column maxima of b
-  float* out;          // [R, I, K]
+  const float* m_ws;       // [R, K] clamped column maxima of b (read only when fused_max == 0)
+  float* out;              // [R, I, K]
   int64_t out_s0, out_s1;  // element strides of out (innermost stride is 1)
   int R, I, J, K;
   int tiles_m, tiles_n, num_tiles;
+  int fused_max;
   int* status;
 };
 
-template <int BN_, int MT_, int PREC_, int NS_, int NR_, int NTW_>
+template <int BN_, int MT_, int PREC_, int NS_>
 struct Lm2expCfg {
-  static constexpr int BM = 128, BK = 32;
-  static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_, NR = NR_, NTW = NTW_;
+  static constexpr int BM = 128, BK = 32, NTW = 8;
+  static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_;
   static constexpr int NCOPY = PREC ? 2 : 1;               // hi (+ lo) copies of each operand
   static constexpr int A_TILE = BM * BK * 4;               // 16 KB
-  static constexpr int B_TILE = BN * BK * 4;
+  static constexpr int B_BOX = 32 * BK * 4;                // one 32-column group: 4 KB
+  static constexpr int NGRP = BN / 32;
+  static constexpr int B_TILE = NGRP * B_BOX;
   static constexpr int STAGE = NCOPY * (MT * A_TILE + B_TILE);
-  static constexpr int RAW = BK * BN * 4;
+  static constexpr int RP = NTW / NGRP;                    // warps sharing one column group (row parts)
+  static constexpr int ROWS_PER_WARP = BK / RP;
   static constexpr int ACC_COLS = MT * BN;
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
   static constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256 ? 256 : 512);
   static constexpr int NTHREADS = (8 + NTW) * 32;
-  static constexpr int NTT = NTW * 32;                     // transform threads
-  static constexpr int THR_PER_COL = NTT / BN;             // transform threads sharing one column
-  static constexpr int GROUPS = 8 / THR_PER_COL;           // groups of 4 j-rows per thread per k-block
-  static constexpr int NBAR = 3 * NS + 2 * NR + 4;
-  static constexpr int SMEM_BYTES = 1024 /*align slack*/ + NS * STAGE + NR * RAW + NBAR * 8 + 64;
-  static_assert(NTT % BN == 0 && (8 % THR_PER_COL) == 0 && THR_PER_COL >= 1, "transform thread mapping");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
+  static constexpr int NTT = NTW * 32;
+  static constexpr int EPI_PITCH = 36;                     // floats per staged row (conflict-free, 16-byte aligned)
+  static constexpr int EPI_STAGE = 4 * 32 * EPI_PITCH * 4;
+  static constexpr int MSUM_BYTES = 2 * BN * 4;
+  static constexpr int MPART_BYTES = 2 * NTW * 32 * 4;
+  static constexpr int NBAR = 3 * NS + 7;
+  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + MSUM_BYTES + MPART_BYTES + NBAR * 8 + 64;
+  static_assert(BN == 128 || BN == 256, "BN");
+  static_assert(NTW % NGRP == 0 && ROWS_PER_WARP % 4 == 0, "transform warp mapping");
   static_assert(NBUF * ACC_COLS <= 512, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
@@ -58,23 +73,25 @@ template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const Lm2expParams p) {
-  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS, NR = Cfg::NR;
-  constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW;
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS;
+  constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP, RP = Cfg::RP;
 
   extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment: required by the 128B-swizzled operand tiles.
+  // 1024-byte alignment: required by the 128B-swizzled tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_base = smem;                              // NS stages of [A copies | B copies]
-  uint8_t* raw_base = smem + NS * Cfg::STAGE;              // NR raw b tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw_base + NR * Cfg::RAW);
-  uint64_t* a_full = bars;                 // [NS] TMA bytes of the a-tiles landed
-  uint64_t* b_full = bars + NS;            // [NS] transform warps finished the B operand (and a split)
-  uint64_t* opnd_empty = bars + 2 * NS;    // [NS] MMAs reading the stage retired
-  uint64_t* raw_full = bars + 3 * NS;      // [NR] TMA bytes of the raw b-tile landed
-  uint64_t* raw_empty = raw_full + NR;     // [NR] transform warps done reading the raw tile
-  uint64_t* acc_full = raw_empty + NR;     // [2] accumulator buffer complete
+  uint8_t* stage_base = smem;                                          // NS stages of [A copies | B copies]
+  float* epi_stage = reinterpret_cast<float*>(smem + NS * Cfg::STAGE);  // 4 warps x 32 x EPI_PITCH
+  float* msum = epi_stage + 4 * 32 * Cfg::EPI_PITCH;                   // [2][BN] stabiliser of the tile's columns
+  float* mpart = msum + 2 * BN;                                        // [2][NTW][32] per-warp partial maxima
+  uint64_t* bars = reinterpret_cast<uint64_t*>(mpart + 2 * NTW * 32);
+  uint64_t* full = bars;                   // [NS] TMA bytes of the stage landed
+  uint64_t* xf_done = bars + NS;           // [NS] transform warps finished with the stage
+  uint64_t* stage_empty = bars + 2 * NS;   // [NS] stage may be overwritten
+  uint64_t* acc_full = bars + 3 * NS;      // [2] accumulator buffer complete
   uint64_t* acc_empty = acc_full + 2;      // [2] epilogue drained the buffer
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* msum_empty = acc_empty + 2;    // [2] epilogue finished reading msum[slot]
+  uint64_t* mx_bar = msum_empty + 2;       // [1] all transform warps published their partial maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mx_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -92,18 +109,16 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&a_full[s], 1);
-      mbar_init(&b_full[s], NTW);
-      mbar_init(&opnd_empty[s], 1);
-    }
-    for (int s = 0; s < NR; ++s) {
-      mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], NTW);
+      mbar_init(&full[s], 1);
+      mbar_init(&xf_done[s], NTW);
+      mbar_init(&stage_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 4);
+      mbar_init(&msum_empty[s], 4);
     }
+    mbar_init(mx_bar, NTW);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -117,7 +132,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int KB = (p.J + BK - 1) / BK;  // k-blocks per tile
+  const int KB = (p.J + BK - 1) / BK;  // k-blocks per pass
+  const bool fused = p.fused_max != 0;
 
   // Tile id -> (batch r, column tile, row tile); row tiles vary fastest so CTAs that run together
   // share one b slab in L2.
@@ -138,18 +154,20 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int r, n0, i0;
         decode(tile, r, n0, i0);
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % NS;
-          const uint32_t ph = (it / NS) & 1;
-          if (!(ok = mbar_wait(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
-          mbar_arrive_expect_tx(&a_full[s], MT * Cfg::A_TILE);
+        for (int pass = fused ? 0 : 1; ok && pass < 2; ++pass) {  // 0 = max pass (b only), 1 = contraction
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
+            if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
+            mbar_arrive_expect_tx(&full[s], (pass ? MT * Cfg::A_TILE : 0) + Cfg::B_TILE);
+            if (pass) {
 #pragma unroll
-          for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &a_full[s], kb * BK, i0 + t * BM, r);
-          const int rs = it % NR;
-          const uint32_t rph = (it / NR) & 1;
-          if (!(ok = mbar_wait(&raw_empty[rs], rph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
-          mbar_arrive_expect_tx(&raw_full[rs], Cfg::RAW);
-          tma_load_3d(raw_base + rs * Cfg::RAW, &tmap_b, &raw_full[rs], n0, kb * BK, r);
+              for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
+            }
+#pragma unroll
+            for (int g = 0; g < NGRP; ++g)
+              tma_load_3d(b_tile(s, 0) + g * Cfg::B_BOX, &tmap_b, &full[s], n0 + g * 32, kb * BK, r);
+          }
         }
       }
     }
@@ -157,10 +175,20 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
+      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN) | (1u << 16);  // B operand is MN-major
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+        if (fused) {
+          // Max-pass stages carry no MMA work: hand them back as soon as the transform warps are done.
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
+            if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+            mbar_arrive(&stage_empty[s]);
+          }
+          if (!ok) break;
+        }
         const int buf = tcount % Cfg::NBUF;
         const uint32_t aph = (tcount / Cfg::NBUF) & 1;
         if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
@@ -168,11 +196,11 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (it / NS) & 1;
-          if (!(ok = mbar_wait(&a_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
-          if (!(ok = mbar_wait(&b_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+          if (!(ok = mbar_wait(&full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+          if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
           tc_fence_after_sync();
-          const uint64_t db_hi = umma_desc_k_sw128(smem_u32(b_tile(s, 0)));
-          const uint64_t db_lo = PREC ? umma_desc_k_sw128(smem_u32(b_tile(s, 1))) : 0;
+          const uint64_t db_hi = umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
+          const uint64_t db_lo = PREC ? umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX) : 0;
 #pragma unroll
           for (int t = 0; t < MT; ++t) {
             const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
@@ -180,17 +208,19 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ++ks) {
+              // One MMA consumes 8 contraction values: 32 bytes along a K-major row of A, eight
+              // 128-byte rows (two 512-byte swizzle atoms) of the MN-major B boxes.
               const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
               if (PREC) {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 2 * ks, idesc, acc);
-                umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 2 * ks, idesc, 1u);
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, 1u);
+                umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 64 * ks, idesc, acc);
+                umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 64 * ks, idesc, 1u);
+                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, 1u);
               } else {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, acc);
+                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, acc);
               }
             }
           }
-          umma_commit(&opnd_empty[s]);
+          umma_commit(&stage_empty[s]);
         }
         if (ok) umma_commit(&acc_full[buf]);
       }
@@ -199,6 +229,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    float* stg = epi_stage + q * 32 * Cfg::EPI_PITCH;
+    const int cg = lane & 7, rs = lane >> 3;
     const bool vec_ok = ((p.K & 3) == 0) && ((p.out_s1 & 3) == 0) && ((p.out_s0 & 3) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     uint32_t tcount = 0;
@@ -208,20 +240,21 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       decode(tile, r, n0, i0);
       const int buf = tcount % Cfg::NBUF;
       const uint32_t aph = (tcount / Cfg::NBUF) & 1;
+      const int slot = tcount & 1;
       if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
       tc_fence_after_sync();
+      float* out_r = p.out + static_cast<int64_t>(r) * p.out_s0;
 #pragma unroll 1
       for (int t = 0; t < MT; ++t) {
         if (i0 + t * BM >= p.I) break;  // whole row block is padding
-        const int row = i0 + t * BM + q * 32 + lane;
-        float* out_row = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(row) * p.out_s1;
+        const int rbase = i0 + t * BM + q * 32;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int k0 = n0 + c * 32;
           if (k0 >= p.K) break;  // whole chunk is padding
           uint32_t v[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
-          const float m_lane = (k0 + lane < p.K) ? __ldg(p.m_ws + static_cast<int64_t>(r) * p.K + k0 + lane) : 0.f;
+          const float m_lane = msum[slot * BN + c * 32 + lane];
           tmem_ld_wait();
           float o[32];
 #pragma unroll
@@ -230,16 +263,31 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const float acc = __uint_as_float(v[e]);
             o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
           }
-          if (row < p.I) {
-            if (vec_ok) {
+          if (vec_ok) {
+            // Row `lane` of the 32 x 32 block goes to shared memory, then lane = (row slot, 16-byte chunk)
+            // reads it back so that 8 consecutive lanes store one contiguous 128-byte row segment.
 #pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (k0 + g * 4 < p.K) {
-                  *reinterpret_cast<float4*>(out_row + k0 + g * 4) =
-                      make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+            for (int g = 0; g < 8; ++g) {
+              *reinterpret_cast<float4*>(stg + lane * Cfg::EPI_PITCH + g * 4) =
+                  make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+            }
+            __syncwarp();
+            if (k0 + cg * 4 < p.K) {
+#pragma unroll
+              for (int x = 0; x < 8; ++x) {
+                const int rr = rs + 4 * x;
+                const int row = rbase + rr;
+                if (row < p.I) {
+                  const float4 val = *reinterpret_cast<const float4*>(stg + rr * Cfg::EPI_PITCH + cg * 4);
+                  *reinterpret_cast<float4*>(out_r + static_cast<int64_t>(row) * p.out_s1 + k0 + cg * 4) = val;
                 }
               }
-            } else {
+            }
+            __syncwarp();
+          } else {
+            const int row = rbase + lane;
+            if (row < p.I) {
+              float* out_row = out_r + static_cast<int64_t>(row) * p.out_s1;
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 if (k0 + e < p.K) out_row[k0 + e] = o[e];
@@ -250,81 +298,149 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[buf]);
+        mbar_arrive(&msum_empty[slot]);
+      }
     }
   } else if (warp >= 8) {
-    // ------------------------------------------------------------------ transform: raw b -> B operand
+    // ------------------------------------------------------------------ transform: b boxes -> E operand, in place
+    const int wv = warp - 8;
+    const int grp = wv % NGRP;   // 32-column group of the tile owned by this warp
+    const int rp = wv / NGRP;    // which ROWS_PER_WARP rows of each k-block this warp handles
+    const int c = lane & 7;      // logical 16-byte chunk (4 columns) within the group
+    const int jsub = lane >> 3;  // row slot: 4 rows per step
     const int tt = threadIdx.x - 8 * 32;
-    const int n = tt % BN;                         // column of the tile owned by this thread
-    const int g0 = (tt / BN) * Cfg::GROUPS;        // first group of 4 j-rows owned by this thread
-    uint32_t it = 0;
+    uint32_t it = 0, tcount = 0, max_passes = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
-      const int kcol = n0 + n;
-      const float m_n = (kcol < p.K) ? __ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol) : 0.f;
+      const int col0 = n0 + grp * 32 + c * 4;  // first of this thread's 4 columns
+      float m4[4];
+
+      if (fused) {
+        // ---- max pass: running maximum of this thread's 4 columns over its row slots
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!(ok = mbar_wait_warp(&full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          const uint8_t* box = b_tile(s, 0) + grp * Cfg::B_BOX;
+          const int jrem = p.J - kb * BK;
+#pragma unroll
+          for (int x = 0; x < Cfg::ROWS_PER_WARP / 4; ++x) {
+            const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
+            if (j < jrem) {  // rows past J are zero-filled by TMA and must not enter the maximum
+              const float4 v = *reinterpret_cast<const float4*>(box + sw128_base32_offset(j, c));
+              mx[0] = fmaxf(mx[0], v.x);
+              mx[1] = fmaxf(mx[1], v.y);
+              mx[2] = fmaxf(mx[2], v.z);
+              mx[3] = fmaxf(mx[3], v.w);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xf_done[s]);
+        }
+        if (!ok) break;
+        // fold the four row slots of the warp (lanes c, c+8, c+16, c+24 hold the same columns)
+#pragma unroll
+        for (int sh = 8; sh <= 16; sh <<= 1) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], sh));
+        }
+        if (RP > 1) {
+          // fold the RP warps that share this column group through shared memory (double-buffered by pass)
+          float* part = mpart + (max_passes & 1) * NTW * 32;
+          if (jsub == 0) *reinterpret_cast<float4*>(part + wv * 32 + c * 4) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(mx_bar);
+          if (!(ok = mbar_wait_warp(mx_bar, max_passes & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+#pragma unroll
+          for (int o = 0; o < RP; ++o) {
+            const float4 v = *reinterpret_cast<const float4*>(part + (o * NGRP + grp) * 32 + c * 4);
+            mx[0] = fmaxf(mx[0], v.x);
+            mx[1] = fmaxf(mx[1], v.y);
+            mx[2] = fmaxf(mx[2], v.z);
+            mx[3] = fmaxf(mx[3], v.w);
+          }
+        }
+        ++max_passes;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) m4[x] = clamp_stab(mx[x]);
+      } else {
+        const float* mrow = p.m_ws + static_cast<int64_t>(r) * p.K;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) m4[x] = (col0 + x < p.K) ? __ldg(mrow + col0 + x) : 0.f;
+      }
+
+      // publish the stabiliser of this tile's columns for the epilogue
+      const int slot = tcount & 1;
+      if (rp == 0) {
+        if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        if (jsub == 0)
+          *reinterpret_cast<float4*>(msum + slot * BN + grp * 32 + c * 4) = make_float4(m4[0], m4[1], m4[2], m4[3]);
+      }
+      bool colv[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) colv[x] = col0 + x < p.K;
+
+      // ---- contraction pass: exp in place
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int s = it % NS;
         const uint32_t ph = (it / NS) & 1;
-        const int rs = it % NR;
-        const uint32_t rph = (it / NR) & 1;
-        if (!(ok = mbar_wait_warp(&raw_full[rs], rph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
-        if (!(ok = mbar_wait_warp(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
-        const float* raw = reinterpret_cast<const float*>(raw_base + rs * Cfg::RAW);
-        uint8_t* bh = b_tile(s, 0);
-        uint8_t* bl = b_tile(s, PREC ? 1 : 0);
-        const int jrem = p.J - kb * BK;  // rows of this k-block that exist (>= 32 except in the tail)
+        if (!(ok = mbar_wait_warp(&full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        uint8_t* box_hi = b_tile(s, 0) + grp * Cfg::B_BOX;
+        uint8_t* box_lo = b_tile(s, PREC ? 1 : 0) + grp * Cfg::B_BOX;
+        const int jrem = p.J - kb * BK;
 #pragma unroll
-        for (int gg = 0; gg < Cfg::GROUPS; ++gg) {
-          const int g = g0 + gg;
+        for (int x = 0; x < Cfg::ROWS_PER_WARP / 4; ++x) {
+          const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
+          const uint32_t off = sw128_base32_offset(j, c);
+          const float4 v = *reinterpret_cast<const float4*>(box_hi + off);
+          // Rows past J and columns past K must be exact zeros in the operand: the TMA zero fill is in
+          // log space, and exp(0 - m) is not zero.
+          const bool rowv = j < jrem;
           float e[4];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int jj = g * 4 + x;
-            const float v = raw[jj * BN + n];
-            // Rows past J and columns past K must be exact zeros in the operand: the TMA zero fill is
-            // in log space, and exp(0 - m) is not zero.
-            e[x] = (jj < jrem && kcol < p.K) ? exp_shifted(v, m_n) : 0.f;
-          }
-          const uint32_t off = static_cast<uint32_t>(n) * 128u + ((static_cast<uint32_t>(g) ^ (n & 7u)) << 4);
+          e[0] = (rowv && colv[0]) ? exp_shifted(v.x, m4[0]) : 0.f;
+          e[1] = (rowv && colv[1]) ? exp_shifted(v.y, m4[1]) : 0.f;
+          e[2] = (rowv && colv[2]) ? exp_shifted(v.z, m4[2]) : 0.f;
+          e[3] = (rowv && colv[3]) ? exp_shifted(v.w, m4[3]) : 0.f;
           if (PREC) {
-            float hi[4], lo[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) tf32_split_rn(e[x], hi[x], lo[x]);
-            *reinterpret_cast<float4*>(bh + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<float4*>(bl + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            float4 h, l;
+            tf32_split_rn(e[0], h.x, l.x);
+            tf32_split_rn(e[1], h.y, l.y);
+            tf32_split_rn(e[2], h.z, l.z);
+            tf32_split_rn(e[3], h.w, l.w);
+            *reinterpret_cast<float4*>(box_hi + off) = h;
+            *reinterpret_cast<float4*>(box_lo + off) = l;
           } else {
-            uint4 w;
-            w.x = tf32_round_bits(e[0]);
-            w.y = tf32_round_bits(e[1]);
-            w.z = tf32_round_bits(e[2]);
-            w.w = tf32_round_bits(e[3]);
-            *reinterpret_cast<uint4*>(bh + off) = w;
+            uint4 u;
+            u.x = tf32_round_bits(e[0]);
+            u.y = tf32_round_bits(e[1]);
+            u.z = tf32_round_bits(e[2]);
+            u.w = tf32_round_bits(e[3]);
+            *reinterpret_cast<uint4*>(box_hi + off) = u;
           }
         }
         if (PREC) {
           // Split the a-tiles in place: hi keeps the tf32 bits, lo = a - hi goes to the second copy.
-          if (!(ok = mbar_wait_warp(&a_full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
           float4* ah = reinterpret_cast<float4*>(a_tile(s, 0, 0));
           float4* al = reinterpret_cast<float4*>(a_tile(s, 1, 0));
-          for (int c = tt; c < MT * Cfg::A_TILE / 16; c += Cfg::NTT) {
-            const float4 v = ah[c];
+          for (int ch = tt; ch < MT * Cfg::A_TILE / 16; ch += Cfg::NTT) {
+            const float4 v = ah[ch];
             float4 h, l;
             tf32_split_trunc(v.x, h.x, l.x);
             tf32_split_trunc(v.y, h.y, l.y);
             tf32_split_trunc(v.z, h.z, l.z);
             tf32_split_trunc(v.w, h.w, l.w);
-            ah[c] = h;
-            al[c] = l;
+            ah[ch] = h;
+            al[ch] = l;
           }
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&b_full[s]);
-          mbar_arrive(&raw_empty[rs]);
-        }
+        if (lane == 0) mbar_arrive(&xf_done[s]);
       }
     }
   }

@@ -189,6 +189,31 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major tf32 operand.  The only swizzled layout the tensor core
+// accepts for 32-bit MN-major operands is the 128-byte swizzle with a 32-byte base: rows of 32 consecutive
+// MN elements (128 bytes) per contraction index, 128 bytes apart, in atoms of 4 rows (512 bytes) inside which
+// the 32-byte chunk index is XORed with row % 4 (address bits [5,7) ^= bits [7,9)).  TMA writes exactly this
+// pattern with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  Consecutive 32-element MN groups are
+// `group_stride_bytes` apart (leading byte offset); consecutive 4-row atoms are 512 bytes apart (stride byte
+// offset).  One MMA (8 contraction values) spans two atoms, so advancing the contraction index by 8 adds
+// 1024 bytes, i.e. 64 to the encoded start address.  Used with bit 16 (B is MN-major) set in the instruction
+// descriptor.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128_base32(uint32_t smem_addr, uint32_t group_stride_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((group_stride_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(1) << 61;  // 128-byte swizzle, 32-byte base
+  return d;
+}
+
+// Byte offset of the 16-byte chunk `c` (0..7) of row `j` inside a box of 128-byte rows stored with the
+// 128-byte / 32-byte-base swizzle.
+__device__ __forceinline__ uint32_t sw128_base32_offset(uint32_t j, uint32_t c) {
+  return j * 128u + (((((c >> 1) ^ (j & 3u)) << 1) | (c & 1u)) << 4);
+}
+
 // Instruction descriptor: D = fp32, A = B = tf32, both K-major, dense, no negate.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
