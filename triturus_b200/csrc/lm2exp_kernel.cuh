@@ -244,64 +244,81 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
       tc_fence_after_sync();
       float* out_r = p.out + static_cast<int64_t>(r) * p.out_s0;
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS;
+      // 32-column chunks of this tile that hold real rows / columns, in (row block, column chunk) order;
+      // the TMEM load of the next chunk is in flight while one chunk is processed.
+      const int nt = min(MT, (p.I - i0 + BM - 1) / BM);
+      const int nc = min(BN / 32, (p.K - n0 + 31) / 32);
+      const int nchunks = nt * nc;
+      uint32_t v[2][32];
+      tmem_ld_32x32(tbase, v[0]);
 #pragma unroll 1
-      for (int t = 0; t < MT; ++t) {
-        if (i0 + t * BM >= p.I) break;  // whole row block is padding
-        const int rbase = i0 + t * BM + q * 32;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int k0 = n0 + c * 32;
-          if (k0 >= p.K) break;  // whole chunk is padding
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
-          const float m_lane = msum[slot * BN + c * 32 + lane];
-          tmem_ld_wait();
-          float o[32];
+      for (int idx = 0; idx < nchunks; idx += 2) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float m_e = __shfl_sync(0xffffffffu, m_lane, e);
-            const float acc = __uint_as_float(v[e]);
-            o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
-          }
-          if (vec_ok) {
-            // Row `lane` of the 32 x 32 block goes to shared memory, then lane = (row slot, 16-byte chunk)
-            // reads it back so that 8 consecutive lanes store one contiguous 128-byte row segment.
+        for (int h = 0; h < 2; ++h) {
+          const int cur = idx + h;
+          if (cur < nchunks) {
+            const int t = cur / nc, c = cur - t * nc;
+            tmem_ld_wait();  // chunk `cur` is in v[h]
+            if (cur + 1 < nchunks) {
+              const int t1 = (cur + 1) / nc, c1 = (cur + 1) - t1 * nc;
+              tmem_ld_32x32(tbase + t1 * BN + c1 * 32, v[h ^ 1]);
+            } else {
+              // every accumulator value of this tile is in registers: hand the buffer back to the MMA warp
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+            const int rbase = i0 + t * BM + q * 32;
+            const int k0 = n0 + c * 32;
+            const float4* m4p = reinterpret_cast<const float4*>(msum + slot * BN + c * 32);
+            float o[32];
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
-              *reinterpret_cast<float4*>(stg + lane * Cfg::EPI_PITCH + g * 4) =
-                  make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+              const float4 m4 = m4p[g];  // same address in every lane: broadcast
+              const float a0 = __uint_as_float(v[h][g * 4 + 0]), a1 = __uint_as_float(v[h][g * 4 + 1]);
+              const float a2 = __uint_as_float(v[h][g * 4 + 2]), a3 = __uint_as_float(v[h][g * 4 + 3]);
+              o[g * 4 + 0] = m4.x + (PREC ? logf(a0) : lg2_approx(a0) * LN2_F);
+              o[g * 4 + 1] = m4.y + (PREC ? logf(a1) : lg2_approx(a1) * LN2_F);
+              o[g * 4 + 2] = m4.z + (PREC ? logf(a2) : lg2_approx(a2) * LN2_F);
+              o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
             }
-            __syncwarp();
-            if (k0 + cg * 4 < p.K) {
+            if (vec_ok) {
+              // Row `lane` of the 32 x 32 block goes to shared memory, then lane = (row slot, 16-byte chunk)
+              // reads it back so that 8 consecutive lanes store one contiguous 128-byte row segment.
 #pragma unroll
-              for (int x = 0; x < 8; ++x) {
-                const int rr = rs + 4 * x;
-                const int row = rbase + rr;
-                if (row < p.I) {
-                  const float4 val = *reinterpret_cast<const float4*>(stg + rr * Cfg::EPI_PITCH + cg * 4);
-                  *reinterpret_cast<float4*>(out_r + static_cast<int64_t>(row) * p.out_s1 + k0 + cg * 4) = val;
+              for (int g = 0; g < 8; ++g) {
+                *reinterpret_cast<float4*>(stg + lane * Cfg::EPI_PITCH + g * 4) =
+                    make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+              }
+              __syncwarp();
+              if (k0 + cg * 4 < p.K) {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                  const int rr = rs + 4 * x;
+                  const int row = rbase + rr;
+                  if (row < p.I) {
+                    const float4 val = *reinterpret_cast<const float4*>(stg + rr * Cfg::EPI_PITCH + cg * 4);
+                    *reinterpret_cast<float4*>(out_r + static_cast<int64_t>(row) * p.out_s1 + k0 + cg * 4) = val;
+                  }
                 }
               }
-            }
-            __syncwarp();
-          } else {
-            const int row = rbase + lane;
-            if (row < p.I) {
-              float* out_row = out_r + static_cast<int64_t>(row) * p.out_s1;
+              __syncwarp();
+            } else {
+              const int row = rbase + lane;
+              if (row < p.I) {
+                float* out_row = out_r + static_cast<int64_t>(row) * p.out_s1;
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                if (k0 + e < p.K) out_row[k0 + e] = o[e];
+                for (int e = 0; e < 32; ++e) {
+                  if (k0 + e < p.K) out_row[k0 + e] = o[e];
+                }
               }
             }
           }
         }
       }
-      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&acc_empty[buf]);
-        mbar_arrive(&msum_empty[slot]);
-      }
+      if (lane == 0) mbar_arrive(&msum_empty[slot]);
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: b boxes -> E operand, in place
@@ -328,15 +345,20 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           if (!(ok = mbar_wait_warp(&full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
           const uint8_t* box = b_tile(s, 0) + grp * Cfg::B_BOX;
           const int jrem = p.J - kb * BK;
+          float4 v[Cfg::ROWS_PER_WARP / 4];
+#pragma unroll
+          for (int x = 0; x < Cfg::ROWS_PER_WARP / 4; ++x) {
+            const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
+            v[x] = *reinterpret_cast<const float4*>(box + sw128_base32_offset(j, c));
+          }
 #pragma unroll
           for (int x = 0; x < Cfg::ROWS_PER_WARP / 4; ++x) {
             const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
             if (j < jrem) {  // rows past J are zero-filled by TMA and must not enter the maximum
-              const float4 v = *reinterpret_cast<const float4*>(box + sw128_base32_offset(j, c));
-              mx[0] = fmaxf(mx[0], v.x);
-              mx[1] = fmaxf(mx[1], v.y);
-              mx[2] = fmaxf(mx[2], v.z);
-              mx[3] = fmaxf(mx[3], v.w);
+              mx[0] = fmaxf(mx[0], v[x].x);
+              mx[1] = fmaxf(mx[1], v[x].y);
+              mx[2] = fmaxf(mx[2], v[x].z);
+              mx[3] = fmaxf(mx[3], v[x].w);
             }
           }
           __syncwarp();
@@ -393,35 +415,48 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         uint8_t* box_hi = b_tile(s, 0) + grp * Cfg::B_BOX;
         uint8_t* box_lo = b_tile(s, PREC ? 1 : 0) + grp * Cfg::B_BOX;
         const int jrem = p.J - kb * BK;
+        constexpr int NLD = Cfg::ROWS_PER_WARP / 4;
+        // All loads first, then the arithmetic, then all stores: the stores go to the addresses the loads
+        // came from, so the compiler would otherwise serialise the iterations.
+        float4 v[NLD];
 #pragma unroll
-        for (int x = 0; x < Cfg::ROWS_PER_WARP / 4; ++x) {
+        for (int x = 0; x < NLD; ++x) {
           const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
-          const uint32_t off = sw128_base32_offset(j, c);
-          const float4 v = *reinterpret_cast<const float4*>(box_hi + off);
+          v[x] = *reinterpret_cast<const float4*>(box_hi + sw128_base32_offset(j, c));
+        }
+        uint4 hi[NLD];
+        float4 lo[NLD];
+#pragma unroll
+        for (int x = 0; x < NLD; ++x) {
+          const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
           // Rows past J and columns past K must be exact zeros in the operand: the TMA zero fill is in
           // log space, and exp(0 - m) is not zero.
+          // The mask is applied to the input (-inf gives an exact zero) so that the exps themselves
+          // run unconditionally and interleave; a branch around each one would serialise them.
           const bool rowv = j < jrem;
           float e[4];
-          e[0] = (rowv && colv[0]) ? exp_shifted(v.x, m4[0]) : 0.f;
-          e[1] = (rowv && colv[1]) ? exp_shifted(v.y, m4[1]) : 0.f;
-          e[2] = (rowv && colv[2]) ? exp_shifted(v.z, m4[2]) : 0.f;
-          e[3] = (rowv && colv[3]) ? exp_shifted(v.w, m4[3]) : 0.f;
+          e[0] = exp_shifted((rowv && colv[0]) ? v[x].x : -INFINITY, m4[0]);
+          e[1] = exp_shifted((rowv && colv[1]) ? v[x].y : -INFINITY, m4[1]);
+          e[2] = exp_shifted((rowv && colv[2]) ? v[x].z : -INFINITY, m4[2]);
+          e[3] = exp_shifted((rowv && colv[3]) ? v[x].w : -INFINITY, m4[3]);
           if (PREC) {
-            float4 h, l;
-            tf32_split_rn(e[0], h.x, l.x);
-            tf32_split_rn(e[1], h.y, l.y);
-            tf32_split_rn(e[2], h.z, l.z);
-            tf32_split_rn(e[3], h.w, l.w);
-            *reinterpret_cast<float4*>(box_hi + off) = h;
-            *reinterpret_cast<float4*>(box_lo + off) = l;
+            float4 h;
+            tf32_split_rn(e[0], h.x, lo[x].x);
+            tf32_split_rn(e[1], h.y, lo[x].y);
+            tf32_split_rn(e[2], h.z, lo[x].z);
+            tf32_split_rn(e[3], h.w, lo[x].w);
+            hi[x] = make_uint4(__float_as_uint(h.x), __float_as_uint(h.y), __float_as_uint(h.z), __float_as_uint(h.w));
           } else {
-            uint4 u;
-            u.x = tf32_round_bits(e[0]);
-            u.y = tf32_round_bits(e[1]);
-            u.z = tf32_round_bits(e[2]);
-            u.w = tf32_round_bits(e[3]);
-            *reinterpret_cast<uint4*>(box_hi + off) = u;
+            hi[x] = make_uint4(tf32_round_bits(e[0]), tf32_round_bits(e[1]), tf32_round_bits(e[2]),
+                               tf32_round_bits(e[3]));
           }
+        }
+#pragma unroll
+        for (int x = 0; x < NLD; ++x) {
+          const int j = rp * Cfg::ROWS_PER_WARP + 4 * x + jsub;
+          const uint32_t off = sw128_base32_offset(j, c);
+          *reinterpret_cast<uint4*>(box_hi + off) = hi[x];
+          if (PREC) *reinterpret_cast<float4*>(box_lo + off) = lo[x];
         }
         if (PREC) {
           // Split the a-tiles in place: hi keeps the tf32 bits, lo = a - hi goes to the second copy.

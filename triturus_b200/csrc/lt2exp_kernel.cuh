@@ -296,12 +296,17 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
 
       for (int jc = 0; ok && jc < JC; ++jc) {
         // exp(b - mb) for this thread's column and the 32 j of the chunk; zero past J or K.
+        // All 32 loads are issued before the first exp: padding reads as -inf, which exp turns into an exact
+        // zero, so no exp sits behind a branch.
         float eb[32];
 #pragma unroll
         for (int x = 0; x < 32; ++x) {
           const int j = jc * BK + x;
-          eb[x] = (col_ok && j < p.J) ? exp_shifted(__ldg(b_col + static_cast<int64_t>(j) * p.b_s1), mb) : 0.f;
+          eb[x] = -INFINITY;
+          if (col_ok && j < p.J) eb[x] = __ldg(b_col + static_cast<int64_t>(j) * p.b_s1);
         }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) eb[x] = exp_shifted(eb[x], mb);
         // Raw a values of this group's next PF k-blocks.
         float apf[PF];
 #pragma unroll
