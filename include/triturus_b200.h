@@ -52,8 +52,9 @@ const char* triturus_b200_strerror(int code);
  *   precision: TRITURUS_B200_PRECISION_*.
  *   variant:   0 = choose everything from the problem size; otherwise STAB * 100000 + BN * 10 + MT with
  *              BN in {128, 256} output columns and MT in {1, 2} 128-row blocks per CTA tile (BN * 10 + MT
- *              may be 0 = automatic) and STAB selecting where the stabiliser is computed: 0 = automatic,
- *              1 = pre-pass launch writing the workspace, 2 = max pass fused into the contraction kernel.
+ *              may be 0 = automatic; 2564 = a 256 x 256 tile computed by a pair of CTAs, 128 rows each)
+ *              and STAB selecting where the stabiliser is computed: 0 = automatic, 1 = pre-pass launch
+ *              writing the workspace, 2 = max pass fused into the contraction kernel (not with 2564).
  *              (The counterpart of the reference's autotune table, triturus/lm2exp.py:7-58.)
  *   workspace: at least triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned; holds the
  *              [R,K] stabiliser.

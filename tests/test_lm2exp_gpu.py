@@ -12,7 +12,7 @@ from oracle import logspace_oracle as orc
 pytestmark = pytest.mark.gpu
 
 PRECISIONS = ["tf32", "3xtf32"]
-VARIANTS = [0, 1281, 1282, 2561, 2562]
+VARIANTS = [0, 1281, 1282, 2561, 2562, 2564, 101282, 202561]
 
 
 def _run(a, b, **kw):

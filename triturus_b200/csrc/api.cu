@@ -10,6 +10,7 @@
 
 #include "../../include/triturus_b200.h"
 #include "lm2exp_kernel.cuh"
+#include "lm2exp_pair_kernel.cuh"
 #include "lt2exp_kernel.cuh"
 
 namespace tb200 {
@@ -170,6 +171,49 @@ using LmT_256_2 = Lm2expCfg<256, 2, 0, 3>;
 using LmX_128_1 = Lm2expCfg<128, 1, 1, 3>;
 using LmX_128_2 = Lm2expCfg<128, 2, 1, 2>;
 
+using LmPairT = Lm2expPairCfg<0, 6>;
+using LmPairX = Lm2expPairCfg<1, 3>;
+
+// Launch on CTA pairs: a cluster of two CTAs per 256 x 256 tile.
+template <class Cfg>
+static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expParams p, cudaStream_t stream) {
+  auto kern = lm2exp_pair_kernel<Cfg>;
+  static std::once_flag once[64];
+  static cudaError_t attr_rc[64];
+  static int max_clusters[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
+  std::call_once(once[dev], [&] {
+    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    max_clusters[dev] = sm_count() / 2;
+    if (attr_rc[dev] == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
+      cfg.blockDim = dim3(Cfg::NTHREADS, 1, 1);
+      cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) max_clusters[dev] = n;
+    }
+  });
+  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  p.tiles_m = (p.I + 2 * Cfg::BM - 1) / (2 * Cfg::BM);
+  p.tiles_n = (p.K + Cfg::BN - 1) / Cfg::BN;
+  const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
+  if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
+  p.num_tiles = static_cast<int>(nt);
+  const int clusters = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
+  kern<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+}
+
 static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt) {
   return R * ((rows + 128 * mt - 1) / (128 * mt)) * ((cols + bn - 1) / bn);
 }
@@ -266,13 +310,20 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
   int tile_variant = variant % 100000;
   if (stab_mode > 2) return TRITURUS_B200_EINVAL;
-  if (tile_variant == 0) tile_variant = auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  if (tile_variant == 0) {
+    // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
+    // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
+    const bool want_pair = stab_mode != 2 && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
+    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  }
   int bn = tile_variant / 10;
   const int mt = tile_variant % 10;
-  if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
-  if (precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // the hi/lo copies leave room for 128 columns
+  const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
+  if (!pair && ((bn != 128 && bn != 256) || (mt != 1 && mt != 2))) return TRITURUS_B200_EINVAL;
+  if (pair && stab_mode == 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
+  if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
   // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.
-  const bool fused = stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt);
+  const bool fused = !pair && (stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt));
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* m_ws = static_cast<float*>(workspace);
@@ -312,6 +363,10 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   p.fused_max = fused ? 1 : 0;
   p.status = status_dev;
 
+  if (pair) {
+    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, p, st)
+                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, p, st);
+  }
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {
     return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, p, st);
   }

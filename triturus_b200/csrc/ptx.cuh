@@ -98,6 +98,34 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, c
   return __all_sync(0xffffffffu, ok);
 }
 
+// ----------------------------------------------------------------------------- CTA pairs (clusters of two)
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of the same shared-memory object in the CTA with rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+// Arrive on an mbarrier that may live in the other CTA of the pair.  What the waiter consumes afterwards
+// moves through the async proxy (TMA-written tiles, operands read by the tensor core after
+// fence.proxy.async), so the barrier's own ordering suffices and no cluster-scope fence is paid per k-block.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // ----------------------------------------------------------------------------- fences
 
 // Generic-proxy shared-memory writes -> visible to the async proxy (TMA, tcgen05.mma operands).
@@ -154,6 +182,21 @@ __device__ __forceinline__ void tmem_relinquish() {
 
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// The same for a CTA pair: executed by the same warp of both CTAs, allocates the same columns in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
 // 32 lanes x 32 consecutive columns: lane l of the warp receives columns [c, c+32) of TMEM lane
@@ -230,6 +273,38 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, u
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
       "}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Pair MMA: issued by one thread of the leader CTA, executed by the tensor cores of both CTAs.  With
+// M = 256 each CTA supplies its own 128 rows of A and its own half of the N columns of B from the same
+// shared-memory offsets, and receives its 128 rows of D in its own TMEM.
+__device__ __forceinline__ void umma_tf32_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive on the mbarrier at `cluster_addr` (this CTA's or, through map_to_cta, the other CTA's) once every
+// pair MMA issued so far by this thread has finished in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+// The same arrival delivered to the mbarrier at this shared-memory offset in every CTA of `cta_mask`
+// (bit i = CTA rank i): one instruction frees a stage in both CTAs of a pair.
+__device__ __forceinline__ void umma_commit_pair_mcast(uint32_t smem_addr, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_addr),
+      "h"(cta_mask)
       : "memory");
 }
 
