@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "../../include/triturus_b200.h"
@@ -142,7 +143,8 @@ static int64_t round_up4(int64_t v) { return (v + 3) & ~int64_t(3); }
 // ----------------------------------------------------------------------------- lm2exp launch
 
 template <class Cfg>
-static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expParams p, cudaStream_t stream) {
+static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, Lm2expParams p,
+                         cudaStream_t stream) {
   auto kern = lm2exp_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -159,7 +161,7 @@ static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expPar
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, to, p);
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
@@ -176,7 +178,8 @@ using LmPairX = Lm2expPairCfg<1, 3>;
 
 // Launch on CTA pairs: a cluster of two CTAs per 256 x 256 tile.
 template <class Cfg>
-static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, Lm2expParams p, cudaStream_t stream) {
+static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, Lm2expParams p,
+                              cudaStream_t stream) {
   auto kern = lm2exp_pair_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -210,7 +213,7 @@ static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, Lm2e
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int clusters = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
-  kern<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, to, p);
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
@@ -324,6 +327,9 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
   // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.
   const bool fused = !pair && (stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt));
+  // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
+  // double-buffered so that the epilogue overlaps the next tile.
+  if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* m_ws = static_cast<float*>(workspace);
@@ -350,7 +356,22 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
     if (rc != TRITURUS_B200_OK) return rc;
   }
 
+  // The epilogue stores through TMA when the result meets the tensor-map rules, else with plain stores.
+  CUtensorMap to;
+  memset(&to, 0, sizeof(to));
+  int64_t tos0 = os0, tos1 = os1;
+  const bool out_tma = aligned16(out) && (K & 3) == 0 && fix_stride(I, tos1, round_up4(K)) &&
+                       fix_stride(R, tos0, round_up4(K) * I);
+  if (out_tma) {
+    const int64_t dims[3] = {K, I, R};
+    const int64_t strides[3] = {1, tos1, tos0};
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tmap(&to, out, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+
   Lm2expParams p;
+  p.out_tma = out_tma ? 1 : 0;
   p.m_ws = m_ws;
   p.out = out;
   p.out_s0 = os0;
@@ -364,14 +385,14 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   p.status = status_dev;
 
   if (pair) {
-    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, p, st)
-                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, p, st);
+    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st)
+                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st);
   }
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {
-    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, p, st);
+    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, to, p, st);
   }
-  if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, p, st);
-  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, p, st);
+  if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st);
+  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st);
 }
 
 }  // extern "C"

@@ -11,8 +11,8 @@
 //
 //   warp 0      TMA producer: per k-block MT a-tiles (128 x 32 fp32, K-major, 128B swizzle) and BN/32 b-boxes.
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.kind::tf32 (M = 128, N = BN, K = 8) and commits.
-//   warps 4-7   epilogue: tcgen05.ld, out = m + log(acc), transposed through shared memory so that every
-//               128-bit store instruction writes four full 128-byte row segments.
+//   warps 4-7   epilogue: tcgen05.ld, out = m + log(acc), staged per warp as a swizzled 32 x 32 box in shared
+//               memory and written by TMA stores (full 128-byte rows, clipped at the edges).
 //   warps 8-15  transform.  Warp w owns the 32-column group w % (BN/32); lane = 8 * row_slot + 16-byte chunk.
 //
 // Stabiliser.  Either m comes from a pre-pass through the caller's workspace, or (fused_max) every tile
@@ -37,6 +37,7 @@ struct Lm2expParams {
   int R, I, J, K;
   int tiles_m, tiles_n, num_tiles;
   int fused_max;
+  int out_tma;              // out meets the TMA rules: the epilogue stores through tmap_out
   int* status;
 };
 
@@ -57,8 +58,7 @@ struct Lm2expCfg {
   static constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256 ? 256 : 512);
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
-  static constexpr int EPI_PITCH = 36;                     // floats per staged row (conflict-free, 16-byte aligned)
-  static constexpr int EPI_STAGE = 4 * 32 * EPI_PITCH * 4;
+  static constexpr int EPI_STAGE = 4 * 32 * 128;           // per epilogue warp one 32 x 32 fp32 box, 128B-swizzled
   static constexpr int MSUM_BYTES = 2 * BN * 4;
   static constexpr int MPART_BYTES = 2 * NTW * 32 * 4;
   static constexpr int NBAR = 3 * NS + 7;
@@ -72,7 +72,7 @@ struct Lm2expCfg {
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-              const Lm2expParams p) {
+              const __grid_constant__ CUtensorMap tmap_out, const Lm2expParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS;
   constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP, RP = Cfg::RP;
 
@@ -80,8 +80,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // 1024-byte alignment: required by the 128B-swizzled tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;                                          // NS stages of [A copies | B copies]
-  float* epi_stage = reinterpret_cast<float*>(smem + NS * Cfg::STAGE);  // 4 warps x 32 x EPI_PITCH
-  float* msum = epi_stage + 4 * 32 * Cfg::EPI_PITCH;                   // [2][BN] stabiliser of the tile's columns
+  uint8_t* epi_stage = smem + NS * Cfg::STAGE;                         // 4 warps x 4 KB, 1024-byte aligned
+  float* msum = reinterpret_cast<float*>(epi_stage + Cfg::EPI_STAGE);  // [2][BN] stabiliser of the tile's columns
   float* mpart = msum + 2 * BN;                                        // [2][NTW][32] per-warp partial maxima
   uint64_t* bars = reinterpret_cast<uint64_t*>(mpart + 2 * NTW * 32);
   uint64_t* full = bars;                   // [NS] TMA bytes of the stage landed
@@ -122,6 +122,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.out_tma) tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -154,6 +155,12 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int r, n0, i0;
         decode(tile, r, n0, i0);
+        // With the fused max pass the next tile's b slab is pulled into L2 while this tile computes, so
+        // that its max pass (the first touch of that slab) streams from L2 instead of waiting on HBM
+        // with only NS stages in flight.
+        int nr = 0, nn0 = 0, ni0 = 0;
+        const bool prefetch_next = fused && tile + static_cast<int>(gridDim.x) < p.num_tiles;
+        if (prefetch_next) decode(tile + gridDim.x, nr, nn0, ni0);
         for (int pass = fused ? 0 : 1; ok && pass < 2; ++pass) {  // 0 = max pass (b only), 1 = contraction
           for (int kb = 0; kb < KB; ++kb, ++it) {
             const int s = it % NS;
@@ -163,6 +170,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             if (pass) {
 #pragma unroll
               for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
+              if (prefetch_next) {
+#pragma unroll
+                for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
+              }
             }
 #pragma unroll
             for (int g = 0; g < NGRP; ++g)
@@ -229,10 +240,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    float* stg = epi_stage + q * 32 * Cfg::EPI_PITCH;
-    const int cg = lane & 7, rs = lane >> 3;
-    const bool vec_ok = ((p.K & 3) == 0) && ((p.out_s1 & 3) == 0) && ((p.out_s0 & 3) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint8_t* stg = epi_stage + q * 4096;  // this warp's staging box
+    const bool use_tma = p.out_tma != 0;
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
@@ -283,27 +292,23 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               o[g * 4 + 2] = m4.z + (PREC ? logf(a2) : lg2_approx(a2) * LN2_F);
               o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
             }
-            if (vec_ok) {
-              // Row `lane` of the 32 x 32 block goes to shared memory, then lane = (row slot, 16-byte chunk)
-              // reads it back so that 8 consecutive lanes store one contiguous 128-byte row segment.
+            if (use_tma) {
+              // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
+              // (16-byte chunk g at position g ^ (row % 8): conflict-free), then one lane hands the box to
+              // the TMA unit, which writes full rows and clips at the tensor's edges.
+              if (lane == 0) tma_store_wait_read<0>();  // the previous box has been read out
+              __syncwarp();
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
-                *reinterpret_cast<float4*>(stg + lane * Cfg::EPI_PITCH + g * 4) =
+                *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
                     make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              fence_proxy_async_smem();
               __syncwarp();
-              if (k0 + cg * 4 < p.K) {
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                  const int rr = rs + 4 * x;
-                  const int row = rbase + rr;
-                  if (row < p.I) {
-                    const float4 val = *reinterpret_cast<const float4*>(stg + rr * Cfg::EPI_PITCH + cg * 4);
-                    *reinterpret_cast<float4*>(out_r + static_cast<int64_t>(row) * p.out_s1 + k0 + cg * 4) = val;
-                  }
-                }
+              if (lane == 0) {
+                tma_store_3d(&tmap_out, stg, k0, rbase, r);
+                tma_store_commit();
               }
-              __syncwarp();
             } else {
               const int row = rbase + lane;
               if (row < p.I) {
@@ -320,6 +325,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&msum_empty[slot]);
     }
+    if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: b boxes -> E operand, in place
     const int wv = warp - 8;

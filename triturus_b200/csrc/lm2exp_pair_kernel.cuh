@@ -40,8 +40,7 @@ struct Lm2expPairCfg {
   static constexpr int TMEM_COLS = 512;
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
-  static constexpr int EPI_PITCH = 36;
-  static constexpr int EPI_STAGE = 4 * 32 * EPI_PITCH * 4;
+  static constexpr int EPI_STAGE = 4 * 32 * 128;
   static constexpr int NBAR = 3 * NS + 4;
   static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + NBAR * 8 + 64;
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
@@ -50,15 +49,15 @@ struct Lm2expPairCfg {
 template <class Cfg>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg::NTHREADS, 1)
 lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const Lm2expParams p) {
+                   const __grid_constant__ CUtensorMap tmap_out, const Lm2expParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BNH = Cfg::BNH, BK = Cfg::BK, NS = Cfg::NS;
   constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  float* epi_stage = reinterpret_cast<float*>(smem + NS * Cfg::STAGE);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + 4 * 32 * Cfg::EPI_PITCH);
+  uint8_t* epi_stage = smem + NS * Cfg::STAGE;  // 4 warps x 4 KB staging boxes, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_STAGE);
   uint64_t* full = bars;                  // [NS] this CTA's TMA bytes landed
   uint64_t* xf_done = bars + NS;          // [NS] (leader's copy is used) transform warps of both CTAs done
   uint64_t* stage_empty = bars + 2 * NS;  // [NS] pair MMAs reading the stage retired (committed by the leader)
@@ -92,6 +91,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.out_tma) tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
@@ -190,10 +190,8 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ epilogue (this CTA's 128 rows x 256 columns)
     const int q = warp & 3;
-    float* stg = epi_stage + q * 32 * Cfg::EPI_PITCH;
-    const int cg = lane & 7, rs = lane >> 3;
-    const bool vec_ok = ((p.K & 3) == 0) && ((p.out_s1 & 3) == 0) && ((p.out_s0 & 3) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint8_t* stg = epi_stage + q * 4096;
+    const bool use_tma = p.out_tma != 0;
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
@@ -242,25 +240,21 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               const float acc = __uint_as_float(v[h][e]);
               o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
             }
-            if (vec_ok) {
+            if (use_tma) {
+              // swizzled 32 x 32 staging box -> TMA store (see lm2exp_kernel.cuh)
+              if (lane == 0) tma_store_wait_read<0>();
+              __syncwarp();
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
-                *reinterpret_cast<float4*>(stg + lane * Cfg::EPI_PITCH + g * 4) =
+                *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
                     make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              fence_proxy_async_smem();
               __syncwarp();
-              if (k0 + cg * 4 < p.K) {
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                  const int rr = rs + 4 * x;
-                  const int row = rbase + rr;
-                  if (row < p.I) {
-                    const float4 val = *reinterpret_cast<const float4*>(stg + rr * Cfg::EPI_PITCH + cg * 4);
-                    *reinterpret_cast<float4*>(out_r + static_cast<int64_t>(row) * p.out_s1 + k0 + cg * 4) = val;
-                  }
-                }
+              if (lane == 0) {
+                tma_store_3d(&tmap_out, stg, k0, rbase, r);
+                tma_store_commit();
               }
-              __syncwarp();
             } else {
               const int row = rbase + lane;
               if (row < p.I) {
@@ -275,6 +269,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
       }
     }
+    if (use_tma && lane == 0) tma_store_wait_all();
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: this CTA's b boxes -> E, in place
     const int wv = warp - 8;
