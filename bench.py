@@ -37,9 +37,21 @@ if str(ROOT) not in sys.path:
 from triturus_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 
 METRIC = "lm2exp/lt2exp effective TFLOP/s"
-# Kernel launches of this library per step: the stabiliser pre-pass and the contraction kernel for
-# lm2exp, the contraction kernel alone for lt2exp.
-LAUNCHES_PER_STEP = {"lm2exp": 2, "lt2exp": 1}
+
+
+def launches_per_step(wl, precision: str, variant: int) -> int:
+    """Kernels of this library launched per step: lt2exp is one kernel; lm2exp is the contraction kernel plus,
+    unless the max pass is fused into it, the stabiliser pre-pass (asked from the library)."""
+    if wl.op == "lt2exp":
+        return 1
+    from triturus_b200 import _native
+
+    d = wl.dims
+    n = _native.LIB.triturus_b200_lm2exp_launches(d["R"], d["I"], d["J"], d["K"], 0 if precision == "tf32" else 1, variant)
+    if n <= 0:
+        raise RuntimeError(f"triturus_b200_lm2exp_launches returned {n}")
+    return int(n)
+
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) taken from
 # the committed ncu summaries under profiles/; None where no capture exists yet.
 NCU_TRAFFIC_BYTES = {}
@@ -148,6 +160,8 @@ def cpu_reference_time(wl, reps: int, warmup: int = 1) -> tuple[float, int, str]
     if wl.op == "lt2exp" and wl.dims["I"] * wl.dims["J"] * wl.dims["K"] * wl.dims["R"] > (1 << 31):
         sample = wl.with_batch(2)
         note = f"R=2 of {wl.dims['R']} batch entries, time scaled by {wl.dims['R'] / 2:g}"
+    # torchrun exports OMP_NUM_THREADS=1; the CPU baseline uses every core this process may run on.
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     xs = make_inputs(sample, seed=0)
     fn = orc.lm2exp_fp32 if wl.op == "lm2exp" else orc.lt2exp_fp32
     for _ in range(warmup):
@@ -373,7 +387,7 @@ def main() -> None:
             "roofline": roof,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},  # fmt: skip
-            "gpu_launches": LAUNCHES_PER_STEP[wl.op] * steps,
+            "gpu_launches": launches_per_step(wl, args.precision, args.variant) * steps,
             "clocks": clocks,
             "wall_s": t_wall,
         }

@@ -60,6 +60,10 @@ const char* triturus_b200_strerror(int code);
  *              [R,K] stabiliser.
  */
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K);
+/* Number of kernels one triturus_b200_lm2exp_f32 call launches for these arguments on the current device:
+ * 2 (stabiliser pre-pass + contraction) or 1 (fused max pass); negative on invalid arguments.  The reference
+ * has no counterpart (its launch count is Triton's business, triturus/lm2exp.py:186-205). */
+int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
                              const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
                              int precision, int variant, void* workspace, size_t workspace_bytes,

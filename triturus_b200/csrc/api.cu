@@ -232,6 +232,43 @@ static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256)
   return 128 * 10 + 1;
 }
 
+// What a call of triturus_b200_lm2exp_f32 will run for a problem size, precision and variant code.
+struct Lm2expPlan {
+  int bn, mt;   // output columns per tile, 128-row blocks per CTA
+  bool pair;    // 256 x 256 tile on a pair of CTAs
+  bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
+};
+
+static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out) {
+  (void)J;
+  if (variant < 0) return TRITURUS_B200_EINVAL;
+  const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
+  int tile_variant = variant % 100000;
+  if (stab_mode > 2) return TRITURUS_B200_EINVAL;
+  if (tile_variant == 0) {
+    // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
+    // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
+    const bool want_pair = stab_mode != 2 && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
+    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  }
+  int bn = tile_variant / 10;
+  const int mt = tile_variant % 10;
+  const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
+  if (!pair && ((bn != 128 && bn != 256) || (mt != 1 && mt != 2))) return TRITURUS_B200_EINVAL;
+  if (pair && stab_mode == 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
+  if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
+  // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.
+  const bool fused = !pair && (stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt));
+  // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
+  // double-buffered so that the epilogue overlaps the next tile.
+  if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
+  out->bn = bn;
+  out->mt = pair ? 4 : mt;
+  out->pair = pair;
+  out->fused = fused;
+  return TRITURUS_B200_OK;
+}
+
 }  // namespace tb200
 
 using namespace tb200;
@@ -277,6 +314,16 @@ int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
+int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
+  if (R <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  Lm2expPlan plan;
+  const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
+  if (rc != TRITURUS_B200_OK) return rc;
+  return plan.fused ? 1 : 2;
+}
+
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K) {
   (void)I;
   (void)J;
@@ -309,27 +356,13 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
   if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
 
-  if (variant < 0) return TRITURUS_B200_EINVAL;
-  const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
-  int tile_variant = variant % 100000;
-  if (stab_mode > 2) return TRITURUS_B200_EINVAL;
-  if (tile_variant == 0) {
-    // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
-    // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
-    const bool want_pair = stab_mode != 2 && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
-    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+  Lm2expPlan plan;
+  {
+    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
+    if (prc != TRITURUS_B200_OK) return prc;
   }
-  int bn = tile_variant / 10;
-  const int mt = tile_variant % 10;
-  const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
-  if (!pair && ((bn != 128 && bn != 256) || (mt != 1 && mt != 2))) return TRITURUS_B200_EINVAL;
-  if (pair && stab_mode == 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
-  if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
-  // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.
-  const bool fused = !pair && (stab_mode == 2 || (stab_mode == 0 && I <= 128 * mt));
-  // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
-  // double-buffered so that the epilogue overlaps the next tile.
-  if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
+  const int bn = plan.bn, mt = plan.mt;
+  const bool pair = plan.pair, fused = plan.fused;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* m_ws = static_cast<float*>(workspace);
