@@ -208,6 +208,59 @@ def run_reference_arm(args, wl) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args) -> None:
+    """The reference's benchmark sweeps (benchmarks/lm2exp.py, benchmarks/lt2exp.py) on one GPU: one JSON line
+    per shape and TF32 setting with the reference's GB/s (input bytes only) beside TFLOP/s, for this library
+    and for the same formula written with torch ops on the GPU (cuBLAS bmm), the reference's "torch" provider."""
+    import triturus_b200 as tb
+    from triturus_b200.sweeps import SWEEPS
+    from triturus_b200.utils import set_tf32_enabled
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    def torch_provider(op):
+        def lm(a, b):
+            m = b.amax(dim=1, keepdim=True).clamp(-1e38, 1e38)
+            return m + torch.bmm(a, (b - m).exp()).log()
+
+        def lt(w, a, b):
+            ma = a.amax(dim=1, keepdim=True).clamp(-1e38, 1e38)
+            mb = b.amax(dim=1, keepdim=True).clamp(-1e38, 1e38)
+            kr = ((a - ma).exp()[:, :, None, :] * (b - mb).exp()[:, None, :, :]).flatten(1, 2)
+            return ma + mb + torch.bmm(w.flatten(2, 3), kr).log()
+
+        return lm if op == "lm2exp" else lt
+
+    def median_ms(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for e0, e1 in evs:
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.median(e0.elapsed_time(e1) for e0, e1 in evs)
+
+    ours = tb.lm2exp if args.sweep == "lm2exp" else tb.lt2exp
+    ref = torch_provider(args.sweep)
+    for allow_tf32 in (False, True):
+        set_tf32_enabled(allow_tf32)
+        for pt in SWEEPS[args.sweep]():
+            xs = pt.make_inputs(dev)
+            ms = median_ms(lambda: ours(*xs), args.steps)
+            ms_t = median_ms(lambda: ref(*xs), max(3, args.steps // 4))
+            print(json.dumps({
+                "sweep": f"{pt.op} ({pt.family}, allow_tf32={allow_tf32})", "dims": pt.dims,
+                "triturus_b200": {"ms": ms, "GB/s": pt.gbps(ms), "TFLOP/s": pt.flops / ms / 1e9},
+                "torch": {"ms": ms_t, "GB/s": pt.gbps(ms_t), "TFLOP/s": pt.flops / ms_t / 1e9},
+            }), flush=True)  # fmt: skip
+    set_tf32_enabled(False)
+    tb.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -222,8 +275,14 @@ def main() -> None:
                     help="only W warm-up and K timed steps: no clock sampling, end-to-end leg or CPU baseline "
                          "(for runs under a profiler, whose printed numbers are never bench values)")
     ap.add_argument("--gather", action="store_true", help="also time an all-gather of the output shards (reported separately)")
+    ap.add_argument("--sweep", choices=["lm2exp", "lt2exp"], default=None,
+                    help="walk the reference's benchmark sweep for one op instead of the headline workload")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+
+    if args.sweep is not None:
+        run_sweep(args)
+        return
 
     if args.impl == "reference":
         run_reference_arm(args, wl)

@@ -221,15 +221,32 @@ static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt)
   return R * ((rows + 128 * mt - 1) / (128 * mt)) * ((cols + bn - 1) / bn);
 }
 
-// Largest tile that still gives every SM at least one tile; otherwise the smallest tile.
-static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256) {
+// Tile shape with the smallest estimated run time: waves x tile work x shared-memory cycles per tensor cycle.
+// All kernels are bound by the shared-memory pipe, and a larger tile moves fewer bytes through it per MAC
+// (the factors are bytes per k-block / 128 B per clock over the k-block's tensor cycles), so a larger tile
+// wins unless it leaves the last wave mostly empty.
+static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256, bool in_place_transform) {
   const int sms = sm_count();
   const int mt_max = rows > 128 ? 2 : 1;
   const int bn_max = (cols > 128 && allow_bn256) ? 256 : 128;
-  if (tile_count(R, rows, cols, bn_max, mt_max) >= sms) return bn_max * 10 + mt_max;
-  if (bn_max == 256 && tile_count(R, rows, cols, 128, mt_max) >= sms) return 128 * 10 + mt_max;
-  if (mt_max == 2 && tile_count(R, rows, cols, bn_max, 1) >= sms) return bn_max * 10 + 1;
-  return 128 * 10 + 1;
+  int best = 1281;
+  double best_cost = 1e300;
+  for (int bn = 128; bn <= bn_max; bn *= 2) {
+    for (int mt = 1; mt <= mt_max; ++mt) {
+      const int64_t waves = (tile_count(R, rows, cols, bn, mt) + sms - 1) / sms;
+      // per k-block: a-tiles in + operand read, b in (+ read + write back when transformed in place),
+      // operand read of b once per row block
+      const double kb_bytes = mt * 16384.0 * 2 + bn * 128.0 * (in_place_transform ? 3 : 1) + bn * 128.0 * mt;
+      const double tensor_cycles = mt * bn * 2.0;  // 128 x bn x 32 MACs at 2048 per clock
+      const double factor = (kb_bytes / 128.0) / tensor_cycles;
+      const double cost = static_cast<double>(waves) * mt * bn * (factor > 1.0 ? factor : 1.0);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best = bn * 10 + mt;
+      }
+    }
+  }
+  return best;
 }
 
 // What a call of triturus_b200_lm2exp_f32 will run for a problem size, precision and variant code.
@@ -249,7 +266,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
     const bool want_pair = stab_mode != 2 && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
-    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32);
+    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32, true);
   }
   int bn = tile_variant / 10;
   const int mt = tile_variant % 10;
@@ -494,7 +511,7 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
       (S > 1 && os1 <= 0) || (R > 1 && os0 <= 0))
     return TRITURUS_B200_EALIGN;
 
-  if (variant == 0) variant = auto_variant(R, S, K, true);
+  if (variant == 0) variant = auto_variant(R, S, K, true, false);
   const int bn = variant / 10, mt = variant % 10;
   if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
 
