@@ -40,16 +40,19 @@ METRIC = "lm2exp/lt2exp effective TFLOP/s"
 
 
 def launches_per_step(wl, precision: str, variant: int) -> int:
-    """Kernels of this library launched per step: lt2exp is one kernel; lm2exp is the contraction kernel plus,
-    unless the max pass is fused into it, the stabiliser pre-pass (asked from the library)."""
-    if wl.op == "lt2exp":
-        return 1
+    """Kernels of this library launched per step, asked from the library: lm2exp is the contraction kernel
+    plus, unless the max pass is fused into it, the stabiliser pre-pass; lt2exp is one kernel, or three
+    (zero-fill, contraction slices, log pass) when the contraction is split over the SMs."""
     from triturus_b200 import _native
 
     d = wl.dims
-    n = _native.LIB.triturus_b200_lm2exp_launches(d["R"], d["I"], d["J"], d["K"], 0 if precision == "tf32" else 1, variant)
+    prec = 0 if precision == "tf32" else 1
+    if wl.op == "lt2exp":
+        n = _native.LIB.triturus_b200_lt2exp_launches(d["R"], d["S"], d["I"], d["J"], d["K"], prec, variant)
+    else:
+        n = _native.LIB.triturus_b200_lm2exp_launches(d["R"], d["I"], d["J"], d["K"], prec, variant)
     if n <= 0:
-        raise RuntimeError(f"triturus_b200_lm2exp_launches returned {n}")
+        raise RuntimeError(f"launch-count query returned {n}")
     return int(n)
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) taken from

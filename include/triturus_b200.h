@@ -75,9 +75,20 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
  * Replaces triturus/lt2exp.py:519-630 (host wrapper), :227-357 (_ker_lt2exp_unsplit) and :365-506
  * (_ker_lt2exp_split); semantics follow baselines/lt2exp.py:4-25.
  *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].
- *   variant: 0 = automatic, otherwise BN * 10 + MT as above.
+ *   variant: 0 = automatic, otherwise SPLIT * 10000 + BN * 10 + MT with BN * 10 + MT as above (0 = automatic)
+ *            and SPLIT the number of slices the contraction over (i, j) of every output tile is cut into, the
+ *            counterpart of the reference's NUM_SPLITS and mode argument (triturus/lt2exp.py:533-541):
+ *            0 = automatic (split when the output tiles would occupy fewer than half the SMs), 1 = never
+ *            (mode "unsplit"), n >= 2 = n slices (fewer if a slice would drop below 16 k-blocks), 9999 = as
+ *            automatic but at least two slices (mode "split").  A split call launches three kernels: zero-fill
+ *            of out, the slices adding their partial sums into out with fp32 reductions (so the last bits
+ *            depend on arrival order, as they do under the reference's spin lock, triturus/lt2exp.py:498-506),
+ *            and the in-place log pass.  Unsplit results are deterministic.
  *   No workspace is needed.
  */
+/* Number of kernels one triturus_b200_lt2exp_f32 call launches for these arguments on the current device
+ * (1, or 3 when the contraction is split); negative on invalid arguments. */
+int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
                              int64_t I, int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
                              const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,

@@ -39,10 +39,94 @@ def test_golden(name, precision):
 
 @pytest.mark.parametrize("mode", ["auto", "split", "unsplit"])
 def test_modes_agree(mode):
+    """The reference's three modes (triturus/lt2exp.py:533-541).  "unsplit" is one deterministic kernel; a
+    split contraction adds its slices with fp32 reductions, so it agrees to rounding, not to the bit."""
     g = load_golden("lt_reftest")
     got = _run(g["w"], g["a"], g["b"], mode=mode, precision="3xtf32")
     base = _run(g["w"], g["a"], g["b"], mode="unsplit", precision="3xtf32")
+    again = _run(g["w"], g["a"], g["b"], mode="unsplit", precision="3xtf32")
+    assert torch.equal(base, again)
+    _assert_close(got, g["w"], g["a"], g["b"], "3xtf32")
+    assert (got - base).abs().max().item() <= ATOL["3xtf32"]
+
+
+def test_deterministic_algorithms_switch_off_the_split():
+    """ensure_reproducibility(determinism=True) (triturus/utils.py:12-31) must give run-to-run identical bits."""
+    g = load_golden("lt_reftest")
+    base = _run(g["w"], g["a"], g["b"], mode="unsplit", precision="3xtf32")
+    torch.use_deterministic_algorithms(True, warn_only=True)
+    try:
+        got = _run(g["w"], g["a"], g["b"], mode="auto", precision="3xtf32")
+    finally:
+        torch.use_deterministic_algorithms(False)
     assert torch.equal(got, base)
+
+
+SPLITS = [2, 3, 7, 16, 64, 9999]
+
+
+@pytest.mark.parametrize("split", SPLITS)
+@pytest.mark.parametrize("tile", [0, 1281, 2562])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_contraction_split(precision, tile, split):
+    """Explicit slice counts on a ragged shape: I not divisible by the slice count, J not a multiple of the
+    32-wide chunk, -inf entries and one all -inf column."""
+    if precision == "3xtf32" and tile == 2562:
+        pytest.skip("no 256 x 256 tile in 3xTF32")
+    g = torch.Generator().manual_seed(100 + split)
+    R, S, I, J, K = 2, 150, 37, 70, 140
+    w = torch.rand(R, S, I, J, generator=g)
+    a = torch.randn(R, I, K, generator=g) * 6.0
+    b = torch.randn(R, J, K, generator=g) * 6.0 - 20.0
+    a[torch.rand(R, I, K, generator=g) < 0.03] = float("-inf")
+    b[1, :, 11] = float("-inf")
+    got = _run(w, a, b, precision=precision, variant=split * 10000 + tile)
+    want = orc.lt2exp_fp64(w, a, b)
+    assert not torch.isnan(got).any()
+    assert torch.all(got[1, :, 11] == float("-inf"))
+    assert torch.equal(got == float("-inf"), want == float("-inf"))
+    _assert_close(got, w, a, b, precision, want)
+
+
+def test_contraction_split_strided_output_rows_untouched():
+    """The zero-fill and log passes of a split launch follow the output strides: padding between the rows of
+    a strided result keeps its contents."""
+    import ctypes
+
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(5)
+    R, S, I, J, K = 2, 40, 24, 64, 72
+    w = torch.rand(R, S, I, J, generator=g).cuda()
+    a = torch.randn(R, I, K, generator=g).cuda()
+    b = torch.randn(R, J, K, generator=g).cuda()
+    buf = torch.full((R, S, K + 8), 7.0, device="cuda")
+    out = buf[:, :, :K]
+    i64 = ctypes.c_int64
+    rc = _native.LIB.triturus_b200_lt2exp_f32(
+        w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), R, S, I, J, K,
+        (i64 * 4)(*w.stride()), (i64 * 3)(*a.stride()), (i64 * 3)(*b.stride()), (i64 * 3)(*out.stride()),
+        1, 8 * 10000, _native._status_word(w.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    _native.check_status()
+    assert _native.LIB.triturus_b200_lt2exp_launches(R, S, I, J, K, 1, 8 * 10000) == 3
+    assert _native.LIB.triturus_b200_lt2exp_launches(R, S, I, J, K, 1, 1 * 10000) == 1
+    assert torch.all(buf[:, :, K:] == 7.0)
+    _assert_close(out.cpu(), w.cpu(), a.cpu(), b.cpu(), "3xtf32")
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_split_few_tiles_long_contraction(precision):
+    """One output tile and a 128 x 128 contraction: the automatic mode spreads the slices over the SMs."""
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(77)
+    w = torch.rand(1, 128, 128, 128, generator=g)
+    a = torch.randn(1, 128, 128, generator=g)
+    b = torch.randn(1, 128, 128, generator=g)
+    assert _native.LIB.triturus_b200_lt2exp_launches(1, 128, 128, 128, 128, 0, 0) == 3
+    got = _run(w, a, b, precision=precision)
+    _assert_close(got, w, a, b, precision)
 
 
 def test_unknown_mode_raises():
@@ -122,9 +206,9 @@ def test_batch_permutation_is_bit_exact():
     w = torch.rand(3, 150, 8, 40, generator=g).cuda()
     a = torch.randn(3, 8, 260, generator=g).cuda()
     b = torch.randn(3, 40, 260, generator=g).cuda()
-    x = torch.ops.triturus.lt2exp(w, a, b, 0, 0)
+    x = torch.ops.triturus.lt2exp(w, a, b, 0, 10000)  # unsplit: the deterministic path
     perm = torch.tensor([1, 2, 0]).cuda()
-    z = torch.ops.triturus.lt2exp(w[perm].contiguous(), a[perm].contiguous(), b[perm].contiguous(), 0, 0)
+    z = torch.ops.triturus.lt2exp(w[perm].contiguous(), a[perm].contiguous(), b[perm].contiguous(), 0, 10000)
     assert torch.equal(z, x[perm])
 
 

@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_strerror",
     "triturus_b200_lm2exp_workspace_bytes",
     "triturus_b200_lm2exp_launches",
+    "triturus_b200_lt2exp_launches",
     "triturus_b200_lm2exp_f32",
     "triturus_b200_lt2exp_f32",
     "triturus_b200_colmax_f32",
@@ -74,6 +75,8 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.triturus_b200_lm2exp_workspace_bytes.argtypes = [c_int64] * 4
     lib.triturus_b200_lm2exp_launches.restype = c_int
     lib.triturus_b200_lm2exp_launches.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int, c_int]
+    lib.triturus_b200_lt2exp_launches.restype = c_int
+    lib.triturus_b200_lt2exp_launches.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]
     lib.triturus_b200_lm2exp_f32.restype = c_int
     lib.triturus_b200_lm2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,

@@ -451,25 +451,76 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
 
 namespace tb200 {
 
+// Slices per tile for the contraction split: enough work items to cover the SMs, each slice at least
+// kMinSliceBlocks k-blocks long so the pipeline fill and the per-item column maxima stay a small part.
+// The i range is cut first (a transform thread keeps its exp(b) registers across a whole i range).
+struct LtSplit {
+  int split_i, split_j;
+};
+
+static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
+  constexpr int kMinSliceBlocks = 16;
+  const int JC = (J + 31) / 32;
+  const int64_t kb = static_cast<int64_t>(JC) * I;
+  int64_t want = request;
+  if (request == 0 || request == 9999) {  // automatic; 9999: automatic, but at least two slices
+    const int sms = sm_count();
+    want = tiles * 2 > sms ? 1 : sms / tiles;
+    if (request == 9999 && want < 2) want = 2;
+  }
+  if (want > kb / kMinSliceBlocks) want = kb / kMinSliceBlocks;
+  if (want < 1) want = 1;
+  LtSplit sp;
+  sp.split_i = static_cast<int>(want < I / 8 ? want : (I / 8 > 0 ? I / 8 : 1));
+  int64_t sj = want / sp.split_i;
+  if (sj > JC) sj = JC;
+  sp.split_j = static_cast<int>(sj < 1 ? 1 : sj);
+  return sp;
+}
+
 template <class Cfg>
-static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, cudaStream_t stream) {
+static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
+                         int* launches_only = nullptr) {
   auto kern = lt2exp_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
-  std::call_once(once[dev], [&] {
-    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-  });
-  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
   p.tiles_m = (p.S + Cfg::BM * Cfg::MT - 1) / (Cfg::BM * Cfg::MT);
   p.tiles_n = (p.K + Cfg::BN - 1) / Cfg::BN;
   const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  const LtSplit sp = lt2exp_split(nt, p.I, p.J, split_request);
+  p.split_i = sp.split_i;
+  p.split_j = sp.split_j;
+  const int64_t items = nt * sp.split_i * sp.split_j;
+  if (items > INT32_MAX) return TRITURUS_B200_EINVAL;
+  p.num_items = static_cast<int>(items);
+  const bool split = sp.split_i * sp.split_j > 1;
+  if (launches_only != nullptr) {
+    *launches_only = split ? 3 : 1;
+    return TRITURUS_B200_OK;
+  }
+  std::call_once(once[dev], [&] {
+    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  });
+  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  if (split) {
+    const int64_t total = static_cast<int64_t>(p.R) * p.S * p.K;
+    const int64_t zb = (total + 255) / 256;
+    lt2exp_zero_kernel<<<static_cast<int>(zb < 4 * sm_count() ? zb : 4 * sm_count()), 256, 0, stream>>>(
+        p.out, p.out_s0, p.out_s1, p.R, p.S, p.K);
+  }
+  const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
   kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tw, p);
+  if (split) {
+    const dim3 fgrid((p.K + 31) / 32, (p.S + 63) / 64, p.R);
+    if (fgrid.y > 65535u) return TRITURUS_B200_EINVAL;
+    if (Cfg::PREC) lt2exp_finish_kernel<1><<<fgrid, 256, 0, stream>>>(p);
+    else lt2exp_finish_kernel<0><<<fgrid, 256, 0, stream>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
@@ -484,6 +535,57 @@ using LtX_256_1 = Lt2expCfg<256, 1, 1, 2, 8>;
 
 }  // namespace tb200
 
+// Decodes SPLIT * 10000 + BN * 10 + MT, filling in the automatic tile shape.
+static int lt2exp_variant(int variant, int64_t R, int64_t S, int64_t K, int* bn, int* mt, int* split) {
+  if (variant < 0) return TRITURUS_B200_EINVAL;
+  *split = variant / 10000;
+  int tile = variant % 10000;
+  if (tile == 0) tile = tb200::auto_variant(R, S, K, true, false);
+  *bn = tile / 10;
+  *mt = tile % 10;
+  if ((*bn != 128 && *bn != 256) || (*mt != 1 && *mt != 2)) return TRITURUS_B200_EINVAL;
+  return TRITURUS_B200_OK;
+}
+
+static int lt2exp_check_dims(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision) {
+  if (R <= 0 || S <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (R > 65535 || S > (1 << 30) || I > (1 << 24) || J > (1 << 24) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
+  if (((J + 31) / 32) * I > (1 << 28)) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  return TRITURUS_B200_OK;
+}
+
+template <class... Args>
+static int lt2exp_dispatch(int precision, int bn, int mt, Args... args) {
+  using namespace tb200;
+  if (precision == TRITURUS_B200_PRECISION_3XTF32) {
+    if (bn == 256 && mt == 1) return launch_lt2exp<LtX_256_1>(args...);
+    return mt == 2 ? launch_lt2exp<LtX_128_2>(args...) : launch_lt2exp<LtX_128_1>(args...);
+  }
+  if (bn == 256) return mt == 2 ? launch_lt2exp<LtT_256_2>(args...) : launch_lt2exp<LtT_256_1>(args...);
+  return mt == 2 ? launch_lt2exp<LtT_128_2>(args...) : launch_lt2exp<LtT_128_1>(args...);
+}
+
+extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
+                                             int variant) {
+  int rc = lt2exp_check_dims(R, S, I, J, K, precision);
+  if (rc != TRITURUS_B200_OK) return rc;
+  int bn, mt, split;
+  rc = lt2exp_variant(variant, R, S, K, &bn, &mt, &split);
+  if (rc != TRITURUS_B200_OK) return rc;
+  tb200::Lt2expParams p{};
+  p.R = static_cast<int>(R);
+  p.S = static_cast<int>(S);
+  p.I = static_cast<int>(I);
+  p.J = static_cast<int>(J);
+  p.K = static_cast<int>(K);
+  int n = 0;
+  CUtensorMap none{};
+  rc = lt2exp_dispatch(precision, bn, mt, none, p, split, static_cast<cudaStream_t>(nullptr), &n);
+  return rc == TRITURUS_B200_OK ? n : rc;
+}
+
 extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
                                         int64_t S, int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
                                         const int64_t a_strides[3], const int64_t b_strides[3],
@@ -492,11 +594,10 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
   if (w == nullptr || a == nullptr || b == nullptr || out == nullptr || w_strides == nullptr ||
       a_strides == nullptr || b_strides == nullptr || out_strides == nullptr)
     return TRITURUS_B200_EINVAL;
-  if (R <= 0 || S <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
-  if (R > 65535 || S > (1 << 30) || I > (1 << 24) || J > (1 << 24) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
-  if (((J + 31) / 32) * I > (1 << 28)) return TRITURUS_B200_EINVAL;
-  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
-    return TRITURUS_B200_EINVAL;
+  {
+    const int rc = lt2exp_check_dims(R, S, I, J, K, precision);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
 
   int64_t ws0 = w_strides[0], ws1 = w_strides[1], ws2 = w_strides[2], ws3 = w_strides[3];
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
@@ -511,9 +612,11 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
       (S > 1 && os1 <= 0) || (R > 1 && os0 <= 0))
     return TRITURUS_B200_EALIGN;
 
-  if (variant == 0) variant = auto_variant(R, S, K, true, false);
-  const int bn = variant / 10, mt = variant % 10;
-  if ((bn != 128 && bn != 256) || (mt != 1 && mt != 2)) return TRITURUS_B200_EINVAL;
+  int bn, mt, split;
+  {
+    const int rc = lt2exp_variant(variant, R, S, K, &bn, &mt, &split);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
 
   CUtensorMap tw;
   {
@@ -542,13 +645,7 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
   p.tiles_m = p.tiles_n = p.num_tiles = 0;
   p.status = status_dev;
 
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (precision == TRITURUS_B200_PRECISION_3XTF32) {
-    if (bn == 256 && mt == 1) return launch_lt2exp<LtX_256_1>(tw, p, st);
-    return mt == 2 ? launch_lt2exp<LtX_128_2>(tw, p, st) : launch_lt2exp<LtX_128_1>(tw, p, st);
-  }
-  if (bn == 256) return mt == 2 ? launch_lt2exp<LtT_256_2>(tw, p, st) : launch_lt2exp<LtT_256_1>(tw, p, st);
-  return mt == 2 ? launch_lt2exp<LtT_128_2>(tw, p, st) : launch_lt2exp<LtT_128_1>(tw, p, st);
+  return lt2exp_dispatch(precision, bn, mt, tw, p, split, static_cast<cudaStream_t>(stream), static_cast<int*>(nullptr));
 }
 
 // ----------------------------------------------------------------------------- lm2exp without caller scratch

@@ -17,6 +17,13 @@
 //   warps 4-7   epilogue: out = (ma + mb) + log(acc).
 //   warps 8+    transform: column maxima of a and b (-inf safe), then the P operand of every k-block.
 //               The NTT / BN thread groups take alternate k-blocks.
+//
+// Contraction split.  A shape with few output tiles (small batch, S and K) would leave most SMs idle while
+// each busy one walks the whole (i, j) range.  The launcher can therefore cut the contraction of every tile
+// into split_j * split_i slices, one work item each.  All slices of a tile use the same stabilisers (the
+// column maxima are taken over the full I and J), so their accumulators add linearly: in split mode the
+// epilogue adds its raw accumulator into the zero-filled output with red.global.add and
+// lt2exp_finish_kernel then turns the sums into (ma + mb) + log(sum) in place.
 #pragma once
 
 #include "ptx.cuh"
@@ -31,6 +38,8 @@ struct Lt2expParams {
   int64_t out_s0, out_s1;
   int R, S, I, J, K;
   int tiles_m, tiles_n, num_tiles;
+  int split_i, split_j;  // slices of the i range and of the j-chunk range per tile (1, 1: no split)
+  int num_items;         // num_tiles * split_i * split_j
   int* status;
 };
 
@@ -132,16 +141,30 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int JC = (p.J + BK - 1) / BK;  // j-chunks
-  const int KB = JC * p.I;             // k-blocks per tile: (jc, i), i fastest
+  const int JC = (p.J + BK - 1) / BK;  // j-chunks; the k-blocks of a work item are (jc, i), i fastest
+  const int nsplit = p.split_i * p.split_j;
+  const bool split_mode = nsplit > 1;
 
-  auto decode = [&](int tile, int& r, int& n0, int& s0) {
+  // Work item -> output tile (r, n0, s0) and contraction slice [jc_lo, jc_hi) x [i_lo, i_hi).
+  struct Slice {
+    int jc_lo, jc_hi, i_lo, i_hi;
+  };
+  auto decode = [&](int item, int& r, int& n0, int& s0) -> Slice {
+    const int tile = item / nsplit;
+    const int sp = item - tile * nsplit;
+    const int pj = sp / p.split_i, pi = sp - pj * p.split_i;
+    Slice sl;
+    sl.jc_lo = static_cast<int>(static_cast<int64_t>(pj) * JC / p.split_j);
+    sl.jc_hi = static_cast<int>(static_cast<int64_t>(pj + 1) * JC / p.split_j);
+    sl.i_lo = static_cast<int>(static_cast<int64_t>(pi) * p.I / p.split_i);
+    sl.i_hi = static_cast<int>(static_cast<int64_t>(pi + 1) * p.I / p.split_i);
     const int tm = tile % p.tiles_m;
     const int rest = tile / p.tiles_m;
     const int tn = rest % p.tiles_n;
     r = rest / p.tiles_n;
     n0 = tn * BN;
     s0 = tm * (BM * MT);
+    return sl;
   };
 
   if (warp == 0) {
@@ -149,11 +172,11 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         int r, n0, s0;
-        decode(tile, r, n0, s0);
-        for (int jc = 0; ok && jc < JC; ++jc) {
-          for (int i = 0; i < p.I; ++i, ++it) {
+        const Slice sl = decode(item, r, n0, s0);
+        for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
+          for (int i = sl.i_lo; i < sl.i_hi; ++i, ++it) {
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
@@ -172,7 +195,10 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+        int r, n0, s0;
+        const Slice sl = decode(item, r, n0, s0);
+        const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
         const int buf = tcount % Cfg::NBUF;
         const uint32_t aph = (tcount / Cfg::NBUF) & 1;
         if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
@@ -215,9 +241,9 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
       int r, n0, s0;
-      decode(tile, r, n0, s0);
+      decode(item, r, n0, s0);
       const int buf = tcount % Cfg::NBUF;
       const uint32_t aph = (tcount / Cfg::NBUF) & 1;
       const int slot = tcount & 1;
@@ -234,6 +260,26 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
           if (k0 >= p.K) break;
           uint32_t v[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
+          if (split_mode) {
+            // Slice of a split contraction: add the raw accumulator into the zero-filled output.
+            tmem_ld_wait();
+            if (row < p.S) {
+              if (vec_ok) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  if (k0 + g * 4 < p.K)
+                    red_add_f32x4(out_row + k0 + g * 4, __uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                  __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                  if (k0 + e < p.K) atomicAdd(out_row + k0 + e, __uint_as_float(v[e]));
+                }
+              }
+            }
+            continue;
+          }
           const float m_lane = msum[slot * BN + c * 32 + lane];
           tmem_ld_wait();
           float o[32];
@@ -276,9 +322,10 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     constexpr int NG = Cfg::NGROUPS;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
       int r, n0, s0;
-      decode(tile, r, n0, s0);
+      const Slice sl = decode(item, r, n0, s0);
+      const int In = sl.i_hi - sl.i_lo;
       const int kcol = n0 + n;
       const bool col_ok = kcol < p.K;
       const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
@@ -294,7 +341,8 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
         msum[slot * BN + n] = ma + mb;
       }
 
-      for (int jc = 0; ok && jc < JC; ++jc) {
+      const float* a_sl = a_col + static_cast<int64_t>(sl.i_lo) * p.a_s1;  // first row of this slice
+      for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
         // exp(b - mb) for this thread's column and the 32 j of the chunk; zero past J or K.
         // All 32 loads are issued before the first exp: padding reads as -inf, which exp turns into an exact
         // zero, so no exp sits behind a branch.
@@ -311,22 +359,22 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
         float apf[PF];
 #pragma unroll
         for (int x = 0; x < PF; ++x) {
-          const int i = grp + x * NG;
-          apf[x] = (col_ok && i < p.I) ? __ldg(a_col + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
+          const int i = grp + x * NG;  // row within the slice
+          apf[x] = (col_ok && i < In) ? __ldg(a_sl + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
         }
-        for (int ib = 0; ok && ib < p.I; ib += PF * NG) {
+        for (int ib = 0; ok && ib < In; ib += PF * NG) {
           float acur[PF];
 #pragma unroll
           for (int x = 0; x < PF; ++x) {
             acur[x] = apf[x];
             const int i = ib + PF * NG + grp + x * NG;
-            apf[x] = (col_ok && i < p.I) ? __ldg(a_col + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
+            apf[x] = (col_ok && i < In) ? __ldg(a_sl + static_cast<int64_t>(i) * p.a_s1) : -INFINITY;
           }
 #pragma unroll
           for (int x = 0; x < PF; ++x) {
             const int i = ib + grp + x * NG;
-            if (i >= p.I) break;
-            const uint32_t my_it = it + static_cast<uint32_t>(i);  // k-block index of (jc, i)
+            if (i >= In) break;
+            const uint32_t my_it = it + static_cast<uint32_t>(i);  // k-block index of (jc, i_lo + i)
             const int s = my_it % NS;
             const uint32_t ph = (my_it / NS) & 1;
             if (!(ok = mbar_wait_warp(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
@@ -376,7 +424,7 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
             if (lane == 0) mbar_arrive(&b_full[s]);
           }
         }
-        it += static_cast<uint32_t>(p.I);
+        it += static_cast<uint32_t>(In);
       }
     }
   }
@@ -393,6 +441,35 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// Zero-fills the (possibly strided) output before a split launch accumulates into it.
+__global__ void lt2exp_zero_kernel(float* out, int64_t out_s0, int64_t out_s1, int R, int S, int K) {
+  const int64_t total = static_cast<int64_t>(R) * S * K;
+  for (int64_t x = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; x < total;
+       x += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(x % K);
+    const int64_t rs = x / K;
+    out[(rs / S) * out_s0 + (rs % S) * out_s1 + k] = 0.0f;
+  }
+}
+
+// Second pass of a split launch: out[r,s,k] = (ma[r,k] + mb[r,k]) + log(out[r,s,k]) in place, with the same
+// clamped column maxima the main kernel used.  Block = 32 columns x 8 row lanes; grid = (K / 32, S / 64, R).
+template <int PREC>
+__global__ void __launch_bounds__(256) lt2exp_finish_kernel(const Lt2expParams p) {
+  const int k = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int r = blockIdx.z;
+  if (k >= p.K) return;
+  const float ma = clamp_stab(column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + k, p.a_s1, p.I));
+  const float mb = clamp_stab(column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + k, p.b_s1, p.J));
+  const float m = ma + mb;
+  const int s_end = min(p.S, (static_cast<int>(blockIdx.y) + 1) * 64);
+  for (int s = blockIdx.y * 64 + (threadIdx.x >> 5); s < s_end; s += 8) {
+    float* o = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(s) * p.out_s1 + k;
+    const float acc = *o;
+    *o = m + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
   }
 }
 

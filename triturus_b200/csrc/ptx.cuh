@@ -379,6 +379,11 @@ __device__ __forceinline__ void tf32_split_trunc(float x, float& hi, float& lo) 
   lo = x - hi;
 }
 
+// Four fp32 additions into global memory with one reduction instruction (address 16-byte aligned).
+__device__ __forceinline__ void red_add_f32x4(float* addr, float x, float y, float z, float w) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
 __device__ __forceinline__ float clamp_stab(float m) { return fminf(fmaxf(m, -STAB_CLAMP), STAB_CLAMP); }
 
 // Byte offset of element (row, col) inside a 128-byte-swizzled K-major tile (rows of 32 fp32).

@@ -23,9 +23,13 @@ def lt2exp(
     w [R,S,I,J], a [R,I,K], b [R,J,K].
 
     Assertions and the `mode` check are the reference's (triturus/lt2exp.py:522-541): an unknown mode
-    raises ValueError.  The reference's "split" mode exists to fill the GPU when R*S*K is small by merging
-    partial sums in log space under a spin lock (triturus/lt2exp.py:498-506); this implementation computes
-    every mode with the same deterministic kernel, so the three modes return identical results.
+    raises ValueError.  The reference's "split" mode fills the GPU when R*S*K is small by cutting the
+    contraction into NUM_SPLITS slices whose partial sums are merged in log space under a spin lock
+    (triturus/lt2exp.py:498-506).  Here the slices share one stabiliser, add their partial sums into the
+    result with fp32 reductions and a small second kernel takes the log.  mode="unsplit" never splits,
+    mode="split" always does, mode="auto" splits when the output tiles would occupy fewer than half the SMs
+    (and never under torch.use_deterministic_algorithms(True), because the order of the reductions is not
+    fixed).  `variant` = SPLIT * 10000 + BN * 10 + MT pins the slice count and the tile shape explicitly.
     """
     assert len(w.shape) == 4
     assert len(a.shape) == len(b.shape) == 3
@@ -44,4 +48,10 @@ def lt2exp(
     prec = resolve_precision(precision)
     if w.numel() == 0 or a.numel() == 0 or b.numel() == 0:
         raise ValueError("lt2exp: empty operands are not supported")
-    return _native.lt2exp_op(w, a, b, prec, int(variant))
+    variant = int(variant)
+    if variant < 10000:  # no explicit slice count: derive it from the mode
+        if mode == "unsplit" or (mode == "auto" and torch.are_deterministic_algorithms_enabled()):
+            variant += 10000
+        elif mode == "split":
+            variant += 9999 * 10000
+    return _native.lt2exp_op(w, a, b, prec, variant)
