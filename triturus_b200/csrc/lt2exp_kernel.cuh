@@ -24,6 +24,14 @@
 // column maxima are taken over the full I and J), so their accumulators add linearly: in split mode the
 // epilogue adds its raw accumulator into the zero-filled output with red.global.add and
 // lt2exp_finish_kernel then turns the sums into (ma + mb) + log(sum) in place.
+//
+// Accumulator promotion (3xTF32 only).  The tensor core adds into its fp32 accumulator with truncation, so a
+// sum of positive terms drifts low by about half an ulp per MMA: ~3e-8 relative per 8 contraction terms,
+// 1e-4 after 32 K terms and 2.5e-3 after 256 K, far more than the 3xTF32 operand error.  In 3xTF32 mode
+// the MMA warp therefore starts a fresh TMEM accumulator every CHUNK k-blocks and the epilogue warps, idle
+// during the main loop, add each finished chunk into a master copy kept in a further TMEM region with
+// round-to-nearest fp32 adds (tcgen05.ld, add, tcgen05.st).  Plain TF32 keeps one chunk per work item: its
+// operand rounding dominates up to ~100 K terms and the reference's TF32 path has the same drift.
 #pragma once
 
 #include "ptx.cuh"
@@ -52,8 +60,13 @@ struct Lt2expCfg {
   static constexpr int B_TILE = BN * BK * 4;
   static constexpr int STAGE = NCOPY * (MT * A_TILE + B_TILE);
   static constexpr int ACC_COLS = MT * BN;
-  static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
-  static constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256 ? 256 : 512);
+  static constexpr bool PROMOTE = PREC != 0;
+  static constexpr int CHUNK = 32;  // k-blocks accumulated by the tensor core before a promotion
+  // Accumulator buffers the MMA warp rotates through, and the master copy behind them when promoting.
+  static constexpr int NBUF = PROMOTE ? ((3 * ACC_COLS <= 512) ? 2 : 1) : ((2 * ACC_COLS <= 512) ? 2 : 1);
+  static constexpr int MASTER_COL = NBUF * ACC_COLS;
+  static constexpr int TMEM_USED = (NBUF + (PROMOTE ? 1 : 0)) * ACC_COLS;
+  static constexpr int TMEM_COLS = (TMEM_USED <= 128) ? 128 : (TMEM_USED <= 256 ? 256 : 512);
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
   static constexpr int NGROUPS = NTT / BN;      // transform thread groups taking alternate k-blocks
@@ -61,7 +74,7 @@ struct Lt2expCfg {
   static constexpr int NBAR = 3 * NS + 6;
   static constexpr int SMEM_BYTES = 1024 + NS * STAGE + 2 * BN * 4 + NBAR * 8 + 64;
   static_assert(NTT % BN == 0 && NGROUPS >= 1, "transform thread mapping");
-  static_assert(NBUF * ACC_COLS <= 512, "TMEM capacity");
+  static_assert(TMEM_USED <= 512, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
@@ -193,44 +206,50 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, ccount = 0;  // k-blocks and accumulation chunks issued so far
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         int r, n0, s0;
         const Slice sl = decode(item, r, n0, s0);
         const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
-        const int buf = tcount % Cfg::NBUF;
-        const uint32_t aph = (tcount / Cfg::NBUF) & 1;
-        if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
-        tc_fence_after_sync();
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % NS;
-          const uint32_t ph = (it / NS) & 1;
-          if (!(ok = mbar_wait(&a_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
-          if (!(ok = mbar_wait(&b_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+        const int nch = Cfg::PROMOTE ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
+        int kb = 0;
+        for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
+          const int buf = ccount % Cfg::NBUF;
+          const uint32_t aph = (ccount / Cfg::NBUF) & 1;
+          if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
           tc_fence_after_sync();
-          const uint64_t db_hi = umma_desc_k_sw128(smem_u32(b_tile(s, 0)));
-          const uint64_t db_lo = PREC ? umma_desc_k_sw128(smem_u32(b_tile(s, 1))) : 0;
+          const int kb0 = kb;
+          const int kb_end = Cfg::PROMOTE ? min(KB, kb0 + Cfg::CHUNK) : KB;
+          for (; kb < kb_end; ++kb, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
+            if (!(ok = mbar_wait(&a_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+            if (!(ok = mbar_wait(&b_full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+            tc_fence_after_sync();
+            const uint64_t db_hi = umma_desc_k_sw128(smem_u32(b_tile(s, 0)));
+            const uint64_t db_lo = PREC ? umma_desc_k_sw128(smem_u32(b_tile(s, 1))) : 0;
 #pragma unroll
-          for (int t = 0; t < MT; ++t) {
-            const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
-            const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
-            const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
+            for (int t = 0; t < MT; ++t) {
+              const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
+              const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
+              const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
 #pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-              const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-              if (PREC) {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 2 * ks, idesc, acc);
-                umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 2 * ks, idesc, 1u);
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, 1u);
-              } else {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, acc);
+              for (int ks = 0; ks < BK / 8; ++ks) {
+                const uint32_t acc = (kb > kb0 || ks > 0) ? 1u : 0u;
+                if (PREC) {
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 2 * ks, idesc, acc);
+                  umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 2 * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, 1u);
+                } else {
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 2 * ks, idesc, acc);
+                }
               }
             }
+            umma_commit(&opnd_empty[s]);
           }
-          umma_commit(&opnd_empty[s]);
+          if (ok) umma_commit(&acc_full[buf]);
         }
-        if (ok) umma_commit(&acc_full[buf]);
       }
     }
     __syncwarp();
@@ -239,79 +258,103 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     const int q = warp & 3;
     const bool vec_ok = ((p.K & 3) == 0) && ((p.out_s1 & 3) == 0) && ((p.out_s0 & 3) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, ccount = 0;
     bool ok = true;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
       int r, n0, s0;
-      decode(item, r, n0, s0);
-      const int buf = tcount % Cfg::NBUF;
-      const uint32_t aph = (tcount / Cfg::NBUF) & 1;
+      const Slice sl = decode(item, r, n0, s0);
+      const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
+      const int nch = Cfg::PROMOTE ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
       const int slot = tcount & 1;
-      if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
-      tc_fence_after_sync();
+      for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
+        const int buf = ccount % Cfg::NBUF;
+        const uint32_t aph = (ccount / Cfg::NBUF) & 1;
+        const bool first = ch == 0, last = ch == nch - 1;
+        if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+        tc_fence_after_sync();
 #pragma unroll 1
-      for (int t = 0; t < MT; ++t) {
-        if (s0 + t * BM >= p.S) break;
-        const int row = s0 + t * BM + q * 32 + lane;
-        float* out_row = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(row) * p.out_s1;
+        for (int t = 0; t < MT; ++t) {
+          if (s0 + t * BM >= p.S) break;
+          const int row = s0 + t * BM + q * 32 + lane;
+          float* out_row = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(row) * p.out_s1;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int k0 = n0 + c * 32;
-          if (k0 >= p.K) break;
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
-          if (split_mode) {
-            // Slice of a split contraction: add the raw accumulator into the zero-filled output.
+          for (int c = 0; c < BN / 32; ++c) {
+            const int k0 = n0 + c * 32;
+            if (k0 >= p.K) break;
+            uint32_t v[32];
+            tmem_ld_32x32(lane_base + buf * Cfg::ACC_COLS + t * BN + c * 32, v);
+            if (Cfg::PROMOTE) {
+              // Chunks after the first are added to the master copy; all but the last are stored back.
+              const uint32_t master = lane_base + Cfg::MASTER_COL + t * BN + c * 32;
+              if (!first) {
+                uint32_t mv[32];
+                tmem_ld_32x32(master, mv);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                  v[e] = __float_as_uint(__fadd_rn(__uint_as_float(v[e]), __uint_as_float(mv[e])));
+              }
+              if (!last) {
+                tmem_ld_wait();
+                tmem_st_32x32(master, v);
+                continue;
+              }
+            }
+            if (split_mode) {
+              // Slice of a split contraction: add the raw accumulator into the zero-filled output.
+              tmem_ld_wait();
+              if (row < p.S) {
+                if (vec_ok) {
+#pragma unroll
+                  for (int g = 0; g < 8; ++g) {
+                    if (k0 + g * 4 < p.K)
+                      red_add_f32x4(out_row + k0 + g * 4, __uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                    __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 32; ++e) {
+                    if (k0 + e < p.K) atomicAdd(out_row + k0 + e, __uint_as_float(v[e]));
+                  }
+                }
+              }
+              continue;
+            }
+            const float m_lane = msum[slot * BN + c * 32 + lane];
             tmem_ld_wait();
+            float o[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float m_e = __shfl_sync(0xffffffffu, m_lane, e);
+              const float acc = __uint_as_float(v[e]);
+              o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
+            }
             if (row < p.S) {
               if (vec_ok) {
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                  if (k0 + g * 4 < p.K)
-                    red_add_f32x4(out_row + k0 + g * 4, __uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
-                                  __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+                  if (k0 + g * 4 < p.K) {
+                    *reinterpret_cast<float4*>(out_row + k0 + g * 4) =
+                        make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
+                  }
                 }
               } else {
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                  if (k0 + e < p.K) atomicAdd(out_row + k0 + e, __uint_as_float(v[e]));
+                  if (k0 + e < p.K) out_row[k0 + e] = o[e];
                 }
-              }
-            }
-            continue;
-          }
-          const float m_lane = msum[slot * BN + c * 32 + lane];
-          tmem_ld_wait();
-          float o[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float m_e = __shfl_sync(0xffffffffu, m_lane, e);
-            const float acc = __uint_as_float(v[e]);
-            o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
-          }
-          if (row < p.S) {
-            if (vec_ok) {
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (k0 + g * 4 < p.K) {
-                  *reinterpret_cast<float4*>(out_row + k0 + g * 4) =
-                      make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
-                }
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                if (k0 + e < p.K) out_row[k0 + e] = o[e];
               }
             }
           }
         }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&acc_empty[buf]);
-        mbar_arrive(&msum_empty[slot]);
+        if (Cfg::PROMOTE && !last) tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&acc_empty[buf]);
+          if (last) mbar_arrive(&msum_empty[slot]);
+        }
       }
     }
   } else if (warp >= 8) {
