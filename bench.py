@@ -370,13 +370,15 @@ def main() -> None:
         return
 
     # ---------------------------------------------------------------- end to end from pinned host memory
+    # The call a user with host-resident data makes: the pipelined host entry point (copy-in, kernels and
+    # copy-out of successive batch chunks overlap on three streams); every byte still crosses the bus inside
+    # the timed region.
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     e2e_steps = max(3, min(steps, 10))
+    host_fn = tb.lm2exp_host if wl.op == "lm2exp" else tb.lt2exp_host
 
     def e2e_step() -> None:
-        dev_in = [t.to(dev, non_blocking=True) for t in host_inputs]
-        res = step(*dev_in)
-        host_out.copy_(res, non_blocking=True)
+        host_fn(*host_inputs, out=host_out, precision=args.precision, variant=args.variant)
 
     for _ in range(2):
         e2e_step()

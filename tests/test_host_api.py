@@ -144,3 +144,22 @@ def test_workload_generators_are_seeded_and_shaped():
     assert torch.isinf(b1).float().mean() > 0.005
     assert WORKLOADS["cfg2"].flops == 2.0 * 32 * 1024**3
     assert WORKLOADS["cfg5"].bytes == 4.0 * 64 * (256 * 128 * 128 + 2 * 128 * 4096 + 256 * 4096)
+
+
+def test_host_pipeline_chunking():
+    from triturus_b200.host import chunk_bounds
+
+    assert len(chunk_bounds(32, 12 << 20)) == 12  # 384 MB of input in ~32 MB chunks
+    for batch, chunks in ((7, 3), (5, 16), (1, None), (64, None), (3, 1)):
+        bounds = chunk_bounds(batch, 1 << 20, chunks)
+        assert bounds[0][0] == 0 and bounds[-1][1] == batch
+        assert all(lo < hi for lo, hi in bounds)
+        assert all(bounds[i][1] == bounds[i + 1][0] for i in range(len(bounds) - 1))
+        sizes = [hi - lo for lo, hi in bounds]
+        assert max(sizes) - min(sizes) <= 1
+        if chunks is not None:
+            assert len(bounds) == min(chunks, batch)
+    assert len(chunk_bounds(1000, 1 << 30)) == 16
+    assert len(chunk_bounds(4, 1 << 10)) == 1
+    with pytest.raises(ValueError):
+        chunk_bounds(0, 4)

@@ -7,6 +7,7 @@ registers `torch.ops.triturus.lm2exp` / `torch.ops.triturus.lt2exp`.  There is n
 from . import lm2exp as _lm2exp_module
 from . import lt2exp as _lt2exp_module
 from ._native import NativeLibraryError, check_status, colmax
+from .host import lm2exp_host, lt2exp_host
 from .lm2exp import lm2exp
 from .lt2exp import lt2exp
 from .utils import (
@@ -24,6 +25,8 @@ __all__ = [
     "is_torch_tf32_enabled",
     "is_triturus_tf32_enabled",
     "lm2exp",
+    "lm2exp_host",
     "lt2exp",
+    "lt2exp_host",
     "set_tf32_enabled",
 ]

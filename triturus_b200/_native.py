@@ -111,8 +111,13 @@ def _check(rc: int, what: str) -> None:
         raise NativeLibraryError(f"{what} failed with code {rc}: {strerror(rc)}")
 
 
+_I64x3 = c_int64 * 3
+_I64x4 = c_int64 * 4
+
+
 def _i64(vals) -> ctypes.Array:
-    return (c_int64 * len(vals))(*[int(v) for v in vals])
+    n = len(vals)
+    return _I64x3(*vals) if n == 3 else _I64x4(*vals) if n == 4 else (c_int64 * n)(*vals)
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
@@ -191,6 +196,30 @@ def colmax(x: torch.Tensor) -> torch.Tensor:
     return m
 
 
+class _on_device:
+    """Make `device` current for the duration of a launch; free when it already is (the common case)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self) -> int:
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self.idx
+
+    def __exit__(self, *exc) -> None:
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+
+
+_raw_stream = torch._C._cuda_getCurrentRawStream  # cudaStream_t of torch's current stream, as an int
+
+
 def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
     _require_cuda(a, b)
     R, I, J = a.shape
@@ -200,13 +229,12 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
     ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=a.device)
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
+    with _on_device(a.device) as idx:
         rc = LIB.triturus_b200_lm2exp_f32(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K,
             _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
             int(precision), int(variant), ws.data_ptr(), ws_bytes,
-            _status_word(a.device).data_ptr(), stream,
+            _status_word(a.device).data_ptr(), _raw_stream(idx),
         )  # fmt: skip
     _check(rc, "triturus_b200_lm2exp_f32")
     return out
@@ -220,12 +248,11 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
     a = _inner_contiguous(a)
     b = _inner_contiguous(b)
     out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)
-    with torch.cuda.device(a.device):
-        stream = torch.cuda.current_stream(a.device).cuda_stream
+    with _on_device(a.device) as idx:
         rc = LIB.triturus_b200_lt2exp_f32(
             w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), R, S, I, J, K,
             _i64(w.stride()), _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
-            int(precision), int(variant), _status_word(a.device).data_ptr(), stream,
+            int(precision), int(variant), _status_word(a.device).data_ptr(), _raw_stream(idx),
         )  # fmt: skip
     _check(rc, "triturus_b200_lt2exp_f32")
     return out
@@ -237,6 +264,20 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
 
 lm2exp_op = torch.library.custom_op("triturus::lm2exp", _lm2exp_impl, mutates_args=(), device_types="cuda")
 lt2exp_op = torch.library.custom_op("triturus::lt2exp", _lt2exp_impl, mutates_args=(), device_types="cuda")
+
+
+def lm2exp_call(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
+    """Eager calls go straight to the C ABI (the dispatcher round trip of a Python custom op costs more than
+    the kernel of a small problem); under torch.compile the registered op is what gets traced."""
+    if torch.compiler.is_compiling():
+        return lm2exp_op(a, b, precision, variant)
+    return _lm2exp_impl(a, b, precision, variant)
+
+
+def lt2exp_call(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
+    if torch.compiler.is_compiling():
+        return lt2exp_op(w, a, b, precision, variant)
+    return _lt2exp_impl(w, a, b, precision, variant)
 
 
 @lm2exp_op.register_fake

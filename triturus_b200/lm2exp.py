@@ -25,4 +25,4 @@ def lm2exp(a: torch.Tensor, b: torch.Tensor, *, precision: str | None = None, va
     prec = resolve_precision(precision)
     if a.numel() == 0 or b.numel() == 0:
         raise ValueError("lm2exp: empty operands are not supported")
-    return _native.lm2exp_op(a, b, prec, int(variant))
+    return _native.lm2exp_call(a, b, prec, int(variant))

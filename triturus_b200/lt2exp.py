@@ -54,4 +54,4 @@ def lt2exp(
             variant += 10000
         elif mode == "split":
             variant += 9999 * 10000
-    return _native.lt2exp_op(w, a, b, prec, variant)
+    return _native.lt2exp_call(w, a, b, prec, variant)
