@@ -280,8 +280,19 @@ def main() -> None:
     ap.add_argument("--gather", action="store_true", help="also time an all-gather of the output shards (reported separately)")
     ap.add_argument("--sweep", choices=["lm2exp", "lt2exp"], default=None,
                     help="walk the reference's benchmark sweep for one op instead of the headline workload")
+    ap.add_argument("--dims", default=None,
+                    help="override dimensions of the chosen workload, e.g. R=1,S=512,I=512,J=512,K=512 "
+                         "(same input distribution; for profiling other shapes, not a headline number)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    custom_dims = False
+    if args.dims:
+        over = {k.strip(): int(v) for k, v in (kv.split("=") for kv in args.dims.split(","))}
+        unknown = set(over) - set(wl.dims)
+        if unknown:
+            raise SystemExit(f"--dims: {sorted(unknown)} are not dimensions of {wl.name} ({sorted(wl.dims)})")
+        wl = type(wl)(wl.name, wl.op, {**wl.dims, **over}, wl.description)
+        custom_dims = True
 
     if args.sweep is not None:
         run_sweep(args)
@@ -446,7 +457,7 @@ def main() -> None:
             achieved = wl.bytes / (launch_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "peak_source": f"stream copy, {peaks['source']}"}  # fmt: skip
-        roof["traffic"] = NCU_TRAFFIC_BYTES.get((wl.name, args.precision))
+        roof["traffic"] = None if custom_dims else NCU_TRAFFIC_BYTES.get((wl.name, args.precision))
         roof["launch_ms"] = launch_ms
         roof["prepass_ms"] = prepass_ms
         roof["kernel"] = ("lt2exp_kernel" if wl.op == "lt2exp" else
@@ -467,7 +478,7 @@ def main() -> None:
             "dtype": "tf32" if args.precision == "tf32" else "3xtf32",
             "data": "synthetic",
             "config": {
-                "workload": f"{wl.name}: {wl.op} fp32 {wl.dims} per GPU",
+                "workload": f"{wl.name}{' (custom dims)' if custom_dims else ''}: {wl.op} fp32 {wl.dims} per GPU",
                 "precision": args.precision,
                 "variant": args.variant,
                 "sharding": f"batch r, one full batch per GPU x {world}",

@@ -516,7 +516,7 @@ static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_reques
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
   kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tw, p);
   if (split) {
-    const dim3 fgrid((p.K + 31) / 32, (p.S + 63) / 64, p.R);
+    const dim3 fgrid((p.K + 127) / 128, (p.S + 63) / 64, p.R);
     if (fgrid.y > 65535u) return TRITURUS_B200_EINVAL;
     if (Cfg::PREC) lt2exp_finish_kernel<1><<<fgrid, 256, 0, stream>>>(p);
     else lt2exp_finish_kernel<0><<<fgrid, 256, 0, stream>>>(p);
@@ -643,6 +643,8 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
   p.J = static_cast<int>(J);
   p.K = static_cast<int>(K);
   p.tiles_m = p.tiles_n = p.num_tiles = 0;
+  p.vec_ab = (K % 4 == 0 && aligned16(a) && aligned16(b) && as0 % 4 == 0 && as1 % 4 == 0 && bs0 % 4 == 0 &&
+              bs1 % 4 == 0) ? 1 : 0;
   p.status = status_dev;
 
   return lt2exp_dispatch(precision, bn, mt, tw, p, split, static_cast<cudaStream_t>(stream), static_cast<int*>(nullptr));

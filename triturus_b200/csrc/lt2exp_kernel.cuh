@@ -48,6 +48,7 @@ struct Lt2expParams {
   int tiles_m, tiles_n, num_tiles;
   int split_i, split_j;  // slices of the i range and of the j-chunk range per tile (1, 1: no split)
   int num_items;         // num_tiles * split_i * split_j
+  int vec_ab;            // a and b allow 16-byte loads along k (alignment, strides and K multiples of 4)
   int* status;
 };
 
@@ -71,31 +72,59 @@ struct Lt2expCfg {
   static constexpr int NTT = NTW * 32;
   static constexpr int NGROUPS = NTT / BN;      // transform thread groups taking alternate k-blocks
   static constexpr int GROUP_WARPS = BN / 32;
-  static constexpr int NBAR = 3 * NS + 6;
-  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + 2 * BN * 4 + NBAR * 8 + 64;
+  // Column maxima are taken cooperatively: NTT threads = CQ column quads x RG row groups (16-byte loads).
+  static constexpr int CQ = BN / 4;
+  static constexpr int RG = NTT / CQ;
+  static constexpr int MPART = 2 * RG * BN;  // floats per slot: partial maxima of a and of b
+  static constexpr int NBAR = 3 * NS + 7;
+  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + 2 * BN * 4 + 2 * MPART * 4 + NBAR * 8 + 64;
+  static_assert(NTT % CQ == 0 && RG >= NGROUPS, "column-maximum thread mapping");
   static_assert(NTT % BN == 0 && NGROUPS >= 1, "transform thread mapping");
   static_assert(TMEM_USED <= 512, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
-// max over `rows` elements `stride` apart, sixteen loads in flight.
-__device__ __forceinline__ float column_max(const float* col, int64_t stride, int rows) {
-  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-  int i = 0;
-  for (; i + 16 <= rows; i += 16) {
-    float v[16];
+// Running maximum of four adjacent columns over rows first, first + step, ... < rows, eight 16-byte loads in
+// flight.  `quad` points at row 0 of the four columns.
+__device__ __forceinline__ float4 quad_column_max(const float* quad, int64_t stride, int rows, int first, int step) {
+  float4 m = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+  int i = first;
+  for (; i + 7 * step < rows; i += 8 * step) {
+    float4 v[8];
 #pragma unroll
-    for (int x = 0; x < 16; ++x) v[x] = __ldg(col + static_cast<int64_t>(i + x) * stride);
+    for (int x = 0; x < 8; ++x)
+      v[x] = __ldg(reinterpret_cast<const float4*>(quad + static_cast<int64_t>(i + x * step) * stride));
 #pragma unroll
-    for (int x = 0; x < 16; x += 4) {
-      m0 = fmaxf(m0, v[x]);
-      m1 = fmaxf(m1, v[x + 1]);
-      m2 = fmaxf(m2, v[x + 2]);
-      m3 = fmaxf(m3, v[x + 3]);
+    for (int x = 0; x < 8; ++x) {
+      m.x = fmaxf(m.x, v[x].x);
+      m.y = fmaxf(m.y, v[x].y);
+      m.z = fmaxf(m.z, v[x].z);
+      m.w = fmaxf(m.w, v[x].w);
     }
   }
-  for (; i < rows; ++i) m0 = fmaxf(m0, __ldg(col + static_cast<int64_t>(i) * stride));
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  for (; i < rows; i += step) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(quad + static_cast<int64_t>(i) * stride));
+    m.x = fmaxf(m.x, v.x);
+    m.y = fmaxf(m.y, v.y);
+    m.z = fmaxf(m.z, v.z);
+    m.w = fmaxf(m.w, v.w);
+  }
+  return m;
+}
+
+// Same for one column (the fallback when 16-byte loads are not possible).
+__device__ __forceinline__ float strided_column_max(const float* col, int64_t stride, int rows, int first, int step) {
+  float m = -INFINITY;
+  int i = first;
+  for (; i + 15 * step < rows; i += 16 * step) {
+    float v[16];
+#pragma unroll
+    for (int x = 0; x < 16; ++x) v[x] = __ldg(col + static_cast<int64_t>(i + x * step) * stride);
+#pragma unroll
+    for (int x = 0; x < 16; ++x) m = fmaxf(m, v[x]);
+  }
+  for (; i < rows; i += step) m = fmaxf(m, __ldg(col + static_cast<int64_t>(i) * stride));
+  return m;
 }
 
 template <class Cfg>
@@ -109,14 +138,16 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
   float* msum = reinterpret_cast<float*>(smem + NS * Cfg::STAGE);  // [2][BN]: ma + mb of the tile's columns
-  uint64_t* bars = reinterpret_cast<uint64_t*>(msum + 2 * BN);
+  float* mpart = msum + 2 * BN;  // [2][2][RG][BN] partial column maxima (slot, a|b, row group, column)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(mpart + 2 * Cfg::MPART);
   uint64_t* a_full = bars;               // [NS] w tiles landed
   uint64_t* b_full = bars + NS;          // [NS] P operand (and w split) written
   uint64_t* opnd_empty = bars + 2 * NS;  // [NS] MMAs reading the stage retired
   uint64_t* acc_full = bars + 3 * NS;    // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint64_t* msum_empty = acc_empty + 2;  // [2] epilogue finished reading msum[slot]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(msum_empty + 2);
+  uint64_t* mx_bar = msum_empty + 2;     // [1] every transform warp published its partial maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mx_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -142,6 +173,7 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       mbar_init(&acc_empty[s], 4);
       mbar_init(&msum_empty[s], 4);
     }
+    mbar_init(mx_bar, Cfg::NTW);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
   }
@@ -361,8 +393,8 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     // ------------------------------------------------------------------ transform: P operand generator
     const int tt = threadIdx.x - 8 * 32;
     const int n = tt % BN;       // column of the tile owned by this thread
-    const int grp = tt / BN;     // this thread's group takes k-blocks with i % NGROUPS == grp
     constexpr int NG = Cfg::NGROUPS;
+    const int grp = tt / BN;     // this thread's group takes k-blocks with i % NGROUPS == grp
     uint32_t it = 0, tcount = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
@@ -374,10 +406,37 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
       const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + kcol;
 
-      // Column maxima, clamped as the reference does (baselines/lt2exp.py:15-19): an all -inf column
-      // gets -1e38, its exps are exact zeros and the result is -inf, never NaN.
-      const float ma = clamp_stab(col_ok ? column_max(a_col, p.a_s1, p.I) : -INFINITY);
-      const float mb = clamp_stab(col_ok ? column_max(b_col, p.b_s1, p.J) : -INFINITY);
+      // Column maxima over the full I and J, clamped as the reference does (baselines/lt2exp.py:15-19): an
+      // all -inf column gets -1e38, its exps are exact zeros and the result is -inf, never NaN.  The transform
+      // threads split the rows: with 16-byte loads a thread takes four adjacent columns and every RG-th row,
+      // otherwise its own column and every NG-th row; partial maxima meet in shared memory.
+      float* part = mpart + (tcount & 1) * Cfg::MPART;
+      int nparts;
+      if (p.vec_ab) {
+        const int q = tt % Cfg::CQ, rg = tt / Cfg::CQ;
+        float4 pa = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), pb = pa;
+        if (n0 + 4 * q < p.K) {  // K is a multiple of 4 here: the quad is inside or outside as a whole
+          pa = quad_column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + n0 + 4 * q, p.a_s1, p.I, rg, Cfg::RG);
+          pb = quad_column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + n0 + 4 * q, p.b_s1, p.J, rg, Cfg::RG);
+        }
+        *reinterpret_cast<float4*>(part + rg * BN + 4 * q) = pa;
+        *reinterpret_cast<float4*>(part + (Cfg::RG + rg) * BN + 4 * q) = pb;
+        nparts = Cfg::RG;
+      } else {
+        part[grp * BN + n] = col_ok ? strided_column_max(a_col, p.a_s1, p.I, grp, NG) : -INFINITY;
+        part[(Cfg::RG + grp) * BN + n] = col_ok ? strided_column_max(b_col, p.b_s1, p.J, grp, NG) : -INFINITY;
+        nparts = NG;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(mx_bar);
+      if (!(ok = mbar_wait_warp(mx_bar, tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+      float ma = -INFINITY, mb = -INFINITY;
+      for (int g = 0; g < nparts; ++g) {
+        ma = fmaxf(ma, part[g * BN + n]);
+        mb = fmaxf(mb, part[(Cfg::RG + g) * BN + n]);
+      }
+      ma = clamp_stab(ma);
+      mb = clamp_stab(mb);
       const int slot = tcount & 1;
       if (grp == 0) {
         if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
@@ -499,18 +558,50 @@ __global__ void lt2exp_zero_kernel(float* out, int64_t out_s0, int64_t out_s1, i
 }
 
 // Second pass of a split launch: out[r,s,k] = (ma[r,k] + mb[r,k]) + log(out[r,s,k]) in place, with the same
-// clamped column maxima the main kernel used.  Block = 32 columns x 8 row lanes; grid = (K / 32, S / 64, R).
+// clamped column maxima the main kernel used.  Block = 128 columns x 64 rows of out, 256 threads; the
+// maxima are taken as in the main kernel (32 column quads x 8 row groups with 16-byte loads, or 128 columns x
+// 2 row groups).  Grid = (K / 128, S / 64, R).
 template <int PREC>
 __global__ void __launch_bounds__(256) lt2exp_finish_kernel(const Lt2expParams p) {
-  const int k = blockIdx.x * 32 + (threadIdx.x & 31);
+  __shared__ float part[2][8][128];
+  __shared__ float msum[128];
+  const int k0 = blockIdx.x * 128;
   const int r = blockIdx.z;
-  if (k >= p.K) return;
-  const float ma = clamp_stab(column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + k, p.a_s1, p.I));
-  const float mb = clamp_stab(column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + k, p.b_s1, p.J));
-  const float m = ma + mb;
+  const int tid = threadIdx.x;
+  int nparts;
+  if (p.vec_ab) {
+    const int q = tid & 31, rg = tid >> 5;
+    float4 pa = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), pb = pa;
+    if (k0 + 4 * q < p.K) {
+      pa = quad_column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + k0 + 4 * q, p.a_s1, p.I, rg, 8);
+      pb = quad_column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + k0 + 4 * q, p.b_s1, p.J, rg, 8);
+    }
+    *reinterpret_cast<float4*>(&part[0][rg][4 * q]) = pa;
+    *reinterpret_cast<float4*>(&part[1][rg][4 * q]) = pb;
+    nparts = 8;
+  } else {
+    const int n = tid & 127, g = tid >> 7;
+    const bool col_ok = k0 + n < p.K;
+    part[0][g][n] = col_ok ? strided_column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + k0 + n, p.a_s1, p.I, g, 2) : -INFINITY;
+    part[1][g][n] = col_ok ? strided_column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + k0 + n, p.b_s1, p.J, g, 2) : -INFINITY;
+    nparts = 2;
+  }
+  __syncthreads();
+  if (tid < 128) {
+    float ma = -INFINITY, mb = -INFINITY;
+    for (int g = 0; g < nparts; ++g) {
+      ma = fmaxf(ma, part[0][g][tid]);
+      mb = fmaxf(mb, part[1][g][tid]);
+    }
+    msum[tid] = clamp_stab(ma) + clamp_stab(mb);
+  }
+  __syncthreads();
+  const int n = tid & 127;
+  if (k0 + n >= p.K) return;
+  const float m = msum[n];
   const int s_end = min(p.S, (static_cast<int>(blockIdx.y) + 1) * 64);
-  for (int s = blockIdx.y * 64 + (threadIdx.x >> 5); s < s_end; s += 8) {
-    float* o = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(s) * p.out_s1 + k;
+  for (int s = blockIdx.y * 64 + (tid >> 7); s < s_end; s += 2) {
+    float* o = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(s) * p.out_s1 + k0 + n;
     const float acc = *o;
     *o = m + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
   }
