@@ -75,7 +75,9 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
  * Replaces triturus/lt2exp.py:519-630 (host wrapper), :227-357 (_ker_lt2exp_unsplit) and :365-506
  * (_ker_lt2exp_split); semantics follow baselines/lt2exp.py:4-25.
  *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].
- *   variant: 0 = automatic, otherwise SPLIT * 10000 + BN * 10 + MT with BN * 10 + MT as above (0 = automatic)
+ *   variant: 0 = automatic, otherwise SPLIT * 10000 + BN * 10 + MT with BN * 10 + MT as above (0 = automatic;
+ *            additionally 1283 / 1284 = TF32 only, the generated operand kept in tensor memory instead of
+ *            shared memory, tile 128 columns x 128 / 256 rows; never chosen automatically)
  *            and SPLIT the number of slices the contraction over (i, j) of every output tile is cut into, the
  *            counterpart of the reference's NUM_SPLITS and mode argument (triturus/lt2exp.py:533-541):
  *            0 = automatic (split when the output tiles would occupy fewer than half the SMs), 1 = never

@@ -10,7 +10,7 @@ from oracle import logspace_oracle as orc
 pytestmark = pytest.mark.gpu
 
 PRECISIONS = ["tf32", "3xtf32"]
-VARIANTS = [0, 1281, 1282, 2561, 2562]
+VARIANTS = [0, 1281, 1282, 2561, 2562, 1283, 1284]  # 1283 / 1284: generated operand in TMEM (TF32 only)
 
 
 def _run(w, a, b, **kw):
@@ -66,13 +66,13 @@ SPLITS = [2, 3, 7, 16, 64, 9999]
 
 
 @pytest.mark.parametrize("split", SPLITS)
-@pytest.mark.parametrize("tile", [0, 1281, 2562])
+@pytest.mark.parametrize("tile", [0, 1281, 2562, 1283, 1284])
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_contraction_split(precision, tile, split):
     """Explicit slice counts on a ragged shape: I not divisible by the slice count, J not a multiple of the
     32-wide chunk, -inf entries and one all -inf column."""
-    if precision == "3xtf32" and tile == 2562:
-        pytest.skip("no 256 x 256 tile in 3xTF32")
+    if precision == "3xtf32" and tile in (2562, 1283, 1284):
+        pytest.skip("no 256 x 256 tile and no TMEM-operand kernel in 3xTF32")
     g = torch.Generator().manual_seed(100 + split)
     R, S, I, J, K = 2, 150, 37, 70, 140
     w = torch.rand(R, S, I, J, generator=g)
@@ -140,6 +140,8 @@ def test_unknown_mode_raises():
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_variants_on_ragged_shape(precision, variant):
+    if precision == "3xtf32" and variant in (1283, 1284):
+        pytest.skip("the TMEM-operand kernel is TF32 only")
     g = torch.Generator().manual_seed(9)
     w = torch.rand(3, 270, 13, 37, generator=g)
     a = torch.randn(3, 13, 300, generator=g) * 4.0 + 50.0 * torch.randn(3, 1, 300, generator=g)
@@ -238,3 +240,31 @@ def test_full_size_configs(name, batch, precision):
     assert torch.equal(torch.isfinite(out_s), fin)
     assert (out_s - sa - sb - out)[fin].abs().max().item() <= 2 * ATOL[precision]
     tb.check_status()
+
+
+@pytest.mark.parametrize("variant", [1283, 1284])
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1), (2, 129, 5, 1, 3), (2, 7, 9, 64, 257), (1, 300, 20, 31, 70),
+                                   (3, 256, 16, 40, 384)])
+def test_tmem_operand_kernel_edge_shapes(shape, variant):
+    """The transposed kernel (operand in TMEM) on ragged shapes, with -inf entries and an all -inf column."""
+    R, S, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + variant)
+    w = torch.rand(R, S, I, J, generator=g) + 0.01
+    a = torch.randn(R, I, K, generator=g) * 3.0
+    b = torch.randn(R, J, K, generator=g) * 3.0 - 10.0
+    a[torch.rand(R, I, K, generator=g) < 0.05] = float("-inf")
+    b[R - 1, :, K - 1] = float("-inf")
+    got = _run(w, a, b, precision="tf32", variant=variant)
+    want = orc.lt2exp_fp64(w, a, b)
+    assert not torch.isnan(got).any()
+    assert torch.equal(got == float("-inf"), want == float("-inf"))
+    _assert_close(got, w, a, b, "tf32", want)
+
+
+def test_tmem_operand_kernel_refuses_3xtf32():
+    import triturus_b200 as tb
+
+    w = torch.rand(1, 8, 4, 4).cuda()
+    a = torch.randn(1, 4, 8).cuda()
+    with pytest.raises(tb.NativeLibraryError):
+        tb.lt2exp(w, a, a.clone(), precision="3xtf32", variant=1283)

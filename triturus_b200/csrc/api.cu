@@ -13,6 +13,7 @@
 #include "lm2exp_kernel.cuh"
 #include "lm2exp_pair_kernel.cuh"
 #include "lt2exp_kernel.cuh"
+#include "lt2exp_tmem_kernel.cuh"
 
 namespace tb200 {
 
@@ -478,10 +479,10 @@ static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
   return sp;
 }
 
-template <class Cfg>
-static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
-                         int* launches_only = nullptr) {
-  auto kern = lt2exp_kernel<Cfg>;
+template <class Cfg, void (*Kern)(const CUtensorMap, const Lt2expParams)>
+static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
+                              int* launches_only) {
+  auto kern = Kern;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
   int dev = 0;
@@ -524,6 +525,22 @@ static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_reques
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
+template <class Cfg>
+static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
+                         int* launches_only = nullptr) {
+  return launch_lt2exp_with<Cfg, lt2exp_kernel<Cfg>>(tw, p, split_request, stream, launches_only);
+}
+
+template <class Cfg>
+static int launch_lt2exp_tmem(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
+                              int* launches_only = nullptr) {
+  return launch_lt2exp_with<Cfg, lt2exp_tmem_kernel<Cfg>>(tw, p, split_request, stream, launches_only);
+}
+
+//                              MT NS   (generated operand in TMEM, 128 columns k per tile, TF32)
+using LtM_1 = Lt2expTmemCfg<1, 8>;
+using LtM_2 = Lt2expTmemCfg<2, 6>;
+
 //                          BN   MT PREC NS NTW
 using LtT_128_1 = Lt2expCfg<128, 1, 0, 6, 8>;
 using LtT_128_2 = Lt2expCfg<128, 2, 0, 4, 8>;
@@ -543,6 +560,7 @@ static int lt2exp_variant(int variant, int64_t R, int64_t S, int64_t K, int* bn,
   if (tile == 0) tile = tb200::auto_variant(R, S, K, true, false);
   *bn = tile / 10;
   *mt = tile % 10;
+  if (*bn == 128 && (*mt == 3 || *mt == 4)) return TRITURUS_B200_OK;  // operand in TMEM, 128 / 256 rows
   if ((*bn != 128 && *bn != 256) || (*mt != 1 && *mt != 2)) return TRITURUS_B200_EINVAL;
   return TRITURUS_B200_OK;
 }
@@ -559,6 +577,10 @@ static int lt2exp_check_dims(int64_t R, int64_t S, int64_t I, int64_t J, int64_t
 template <class... Args>
 static int lt2exp_dispatch(int precision, int bn, int mt, Args... args) {
   using namespace tb200;
+  if (mt == 3 || mt == 4) {
+    if (precision != TRITURUS_B200_PRECISION_TF32) return TRITURUS_B200_EINVAL;
+    return mt == 4 ? launch_lt2exp_tmem<LtM_2>(args...) : launch_lt2exp_tmem<LtM_1>(args...);
+  }
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {
     if (bn == 256 && mt == 1) return launch_lt2exp<LtX_256_1>(args...);
     return mt == 2 ? launch_lt2exp<LtX_128_2>(args...) : launch_lt2exp<LtX_128_1>(args...);

@@ -64,6 +64,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// True in exactly one lane of a fully converged warp (the same lane on every call).  Code that the whole warp
+// runs with uniform control flow and that issues its single-thread instructions under this predicate keeps
+// its addresses and descriptors in uniform registers.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Per-CTA abort state shared by all roles.
 struct AbortCtl {
   volatile int* flag;   // shared memory, set once any wait gives up
@@ -349,6 +364,20 @@ __device__ __forceinline__ void umma_commit_pair_mcast(uint32_t smem_addr, uint1
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
           smem_addr),
       "h"(cta_mask)
+      : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from TMEM (lane = row of A, one 32-bit column per
+// contraction index, always K-major); B comes from shared memory through its descriptor.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
