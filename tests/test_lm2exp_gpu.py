@@ -174,3 +174,22 @@ def test_full_size_configs(name, precision):
     out_2 = tb.lm2exp(ad * 4.0, bd, precision=precision)
     assert (out_2 - out - 2.0 * 0.6931471805599453)[fin].abs().max().item() <= 1e-4
     tb.check_status()
+
+
+@pytest.mark.parametrize("variant", [0, 101281, 101282, 201281, 201282])
+@pytest.mark.parametrize("J", [1100, 4096, 16390])
+def test_long_contraction_3xtf32(J, variant):
+    """Contractions longer than 1024 in 3xTF32: the accumulator is re-summed in chunks of 1024 terms with
+    rounded adds, so the result stays within the 3xTF32 tolerance (the tensor core's own fp32 accumulation
+    truncates and would drift low by 2.6e-4 at J = 16 K).  Pre-pass and fused-max variants, one and two row
+    blocks, a ragged last chunk and a ragged last k-block."""
+    g = torch.Generator().manual_seed(J)
+    I = 200 if variant in (0, 101282, 201282) else 100
+    a = torch.rand(2, I, J, generator=g)
+    b = torch.randn(2, J, 140, generator=g)
+    b[1, :, 3] = float("-inf")
+    got = _run(a, b, precision="3xtf32", variant=variant)
+    want = orc.lm2exp_fp64(a, b)
+    assert torch.all(got[1, :, 3] == float("-inf"))
+    res = orc.compare_logspace(got, want, ATOL["3xtf32"])
+    assert res["ok"], res

@@ -258,7 +258,6 @@ struct Lm2expPlan {
 };
 
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out) {
-  (void)J;
   if (variant < 0) return TRITURUS_B200_EINVAL;
   const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
   int tile_variant = variant % 100000;
@@ -266,7 +265,11 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   if (tile_variant == 0) {
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
-    const bool want_pair = stab_mode != 2 && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
+    // (Not for 3xTF32 contractions longer than 1024: only the single-CTA kernel re-sums its accumulator
+    // in chunks, which keeps such sums within the 3xTF32 tolerance.)
+    const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 1024;
+    const bool want_pair =
+        stab_mode != 2 && !long_3x && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32, true);
   }
   int bn = tile_variant / 10;

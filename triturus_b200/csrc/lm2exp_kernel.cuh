@@ -55,7 +55,18 @@ struct Lm2expCfg {
   static constexpr int ROWS_PER_WARP = BK / RP;
   static constexpr int ACC_COLS = MT * BN;
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
-  static constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256 ? 256 : 512);
+  // 3xTF32 only: contractions longer than CHUNK k-blocks are accumulated chunk by chunk and the chunks are
+  // added into a master copy in TMEM with rounded fp32 adds (the tensor core's own accumulation truncates:
+  // measured drift 2.6e-4 in log space at J = 16 K, 2.4e-3 at J = 256 K).  The master copy takes the TMEM
+  // columns from MASTER_COL on; with 256 accumulator columns that is the second buffer, so a promoting
+  // launch runs single-buffered.
+  static constexpr bool PROMOTE = PREC != 0;
+  static constexpr int CHUNK = 32;
+  static constexpr int MASTER_COL = (ACC_COLS <= 128) ? 2 * ACC_COLS : ACC_COLS;
+  static constexpr int NBUF_PROMOTE = (ACC_COLS <= 128) ? 2 : 1;
+  static constexpr int TMEM_USED = PROMOTE ? (MASTER_COL + ACC_COLS) : NBUF * ACC_COLS;
+  static constexpr int TMEM_COLS = (TMEM_USED <= 128) ? 128 : (TMEM_USED <= 256 ? 256 : 512);
+  static_assert(!PROMOTE || ACC_COLS <= 256, "no room for the master copy");
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
   static constexpr int EPI_STAGE = 4 * 32 * 128;           // per epilogue warp one 32 x 32 fp32 box, 128B-swizzled
@@ -65,7 +76,7 @@ struct Lm2expCfg {
   static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + MSUM_BYTES + MPART_BYTES + NBAR * 8 + 64;
   static_assert(BN == 128 || BN == 256, "BN");
   static_assert(NTW % NGRP == 0 && ROWS_PER_WARP % 4 == 0, "transform warp mapping");
-  static_assert(NBUF * ACC_COLS <= 512, "TMEM capacity");
+  static_assert(TMEM_USED <= 512, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
@@ -135,6 +146,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   const int KB = (p.J + BK - 1) / BK;  // k-blocks per pass
   const bool fused = p.fused_max != 0;
+  // Accumulation chunks per tile and the accumulator buffers they rotate through (see Lm2expCfg::PROMOTE).
+  const bool promote = Cfg::PROMOTE && KB > Cfg::CHUNK;
+  const int nch = promote ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
+  const int nbuf = promote ? Cfg::NBUF_PROMOTE : Cfg::NBUF;
 
   // Tile id -> (batch r, column tile, row tile); row tiles vary fastest so CTAs that run together
   // share one b slab in L2.
@@ -187,9 +202,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN) | (1u << 16);  // B operand is MN-major
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, ccount = 0;  // k-block stages and accumulation chunks issued so far
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         if (fused) {
           // Max-pass stages carry no MMA work: hand them back as soon as the transform warps are done.
           for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -200,40 +215,45 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           }
           if (!ok) break;
         }
-        const int buf = tcount % Cfg::NBUF;
-        const uint32_t aph = (tcount / Cfg::NBUF) & 1;
-        if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
-        tc_fence_after_sync();
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % NS;
-          const uint32_t ph = (it / NS) & 1;
-          if (!(ok = mbar_wait(&full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
-          if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+        int kb = 0;
+        for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
+          const int buf = ccount % nbuf;
+          const uint32_t aph = (ccount / nbuf) & 1;
+          if (!(ok = mbar_wait(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
           tc_fence_after_sync();
-          const uint64_t db_hi = umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
-          const uint64_t db_lo = PREC ? umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX) : 0;
+          const int kb0 = kb;
+          const int kb_end = promote ? min(KB, kb0 + Cfg::CHUNK) : KB;
+          for (; kb < kb_end; ++kb, ++it) {
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
+            if (!(ok = mbar_wait(&full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+            if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
+            tc_fence_after_sync();
+            const uint64_t db_hi = umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
+            const uint64_t db_lo = PREC ? umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX) : 0;
 #pragma unroll
-          for (int t = 0; t < MT; ++t) {
-            const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
-            const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
-            const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
+            for (int t = 0; t < MT; ++t) {
+              const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
+              const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
+              const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
 #pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-              // One MMA consumes 8 contraction values: 32 bytes along a K-major row of A, eight
-              // 128-byte rows (two 512-byte swizzle atoms) of the MN-major B boxes.
-              const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-              if (PREC) {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 64 * ks, idesc, acc);
-                umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 64 * ks, idesc, 1u);
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, 1u);
-              } else {
-                umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, acc);
+              for (int ks = 0; ks < BK / 8; ++ks) {
+                // One MMA consumes 8 contraction values: 32 bytes along a K-major row of A, eight
+                // 128-byte rows (two 512-byte swizzle atoms) of the MN-major B boxes.
+                const uint32_t acc = (kb > kb0 || ks > 0) ? 1u : 0u;
+                if (PREC) {
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 64 * ks, idesc, acc);
+                  umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 64 * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, 1u);
+                } else {
+                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, acc);
+                }
               }
             }
+            umma_commit(&stage_empty[s]);
           }
-          umma_commit(&stage_empty[s]);
+          if (ok) umma_commit(&acc_full[buf]);
         }
-        if (ok) umma_commit(&acc_full[buf]);
       }
     }
     __syncwarp();
@@ -242,23 +262,59 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* stg = epi_stage + q * 4096;  // this warp's staging box
     const bool use_tma = p.out_tma != 0;
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, ccount = 0;
     bool ok = true;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
-      const int buf = tcount % Cfg::NBUF;
-      const uint32_t aph = (tcount / Cfg::NBUF) & 1;
       const int slot = tcount & 1;
-      if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
-      tc_fence_after_sync();
-      float* out_r = p.out + static_cast<int64_t>(r) * p.out_s0;
-      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * Cfg::ACC_COLS;
-      // 32-column chunks of this tile that hold real rows / columns, in (row block, column chunk) order;
-      // the TMEM load of the next chunk is in flight while one chunk is processed.
+      // 32-column chunks of this tile that hold real rows / columns, in (row block, column chunk) order.
       const int nt = min(MT, (p.I - i0 + BM - 1) / BM);
       const int nc = min(BN / 32, (p.K - n0 + 31) / 32);
       const int nchunks = nt * nc;
+      int buf = 0;
+      for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
+        buf = ccount % nbuf;
+        const uint32_t aph = (ccount / nbuf) & 1;
+        if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+        tc_fence_after_sync();
+        if (Cfg::PROMOTE && promote) {
+          // Accumulation chunk `ch` of a long contraction: the first one becomes the master copy, the
+          // following ones are added to it, and the last sum is written back over the chunk so that the
+          // output code below finds the whole contraction in `buf`.
+          const bool last = ch == nch - 1;
+          const uint32_t part = lane_base + buf * Cfg::ACC_COLS;
+          const uint32_t master = lane_base + Cfg::MASTER_COL;
+#pragma unroll 1
+          for (int cur = 0; cur < nchunks; ++cur) {
+            const int t = cur / nc, c = cur - t * nc;
+            uint32_t v[32];
+            tmem_ld_32x32(part + t * BN + c * 32, v);
+            if (ch > 0) {
+              uint32_t mv[32];
+              tmem_ld_32x32(master + t * BN + c * 32, mv);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                v[e] = __float_as_uint(__fadd_rn(__uint_as_float(v[e]), __uint_as_float(mv[e])));
+            } else {
+              tmem_ld_wait();
+            }
+            tmem_st_32x32((last ? part : master) + t * BN + c * 32, v);
+          }
+          tmem_st_wait();
+          if (!last) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+        }
+      }
+      if (!ok) break;
+      float* out_r = p.out + static_cast<int64_t>(r) * p.out_s0;
+      const uint32_t tbase = lane_base + buf * Cfg::ACC_COLS;
+      // The TMEM load of the next chunk is in flight while one chunk is processed.
       uint32_t v[2][32];
       tmem_ld_32x32(tbase, v[0]);
 #pragma unroll 1
