@@ -268,3 +268,22 @@ def test_tmem_operand_kernel_refuses_3xtf32():
     a = torch.randn(1, 4, 8).cuda()
     with pytest.raises(tb.NativeLibraryError):
         tb.lt2exp(w, a, a.clone(), precision="3xtf32", variant=1283)
+
+
+@pytest.mark.parametrize("variant", [8 * 10000, 8 * 10000 + 1283])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_contraction_split_odd_columns(precision, variant):
+    """K not a multiple of 4: the column maxima (main kernel and log pass) take the scalar path and the slices
+    add with scalar reductions."""
+    if precision == "3xtf32" and variant % 10000 == 1283:
+        pytest.skip("the TMEM-operand kernel is TF32 only")
+    g = torch.Generator().manual_seed(55)
+    R, S, I, J, K = 2, 70, 40, 50, 141
+    w = torch.rand(R, S, I, J, generator=g)
+    a = torch.randn(R, I, K, generator=g) * 4.0
+    b = torch.randn(R, J, K, generator=g) * 4.0
+    b[0, :, 140] = float("-inf")
+    got = _run(w, a, b, precision=precision, variant=variant)
+    want = orc.lt2exp_fp64(w, a, b)
+    assert torch.all(got[0, :, 140] == float("-inf"))
+    _assert_close(got, w, a, b, precision, want)
