@@ -76,8 +76,9 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
  * (_ker_lt2exp_split); semantics follow baselines/lt2exp.py:4-25.
  *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].
  *   variant: 0 = automatic, otherwise SPLIT * 10000 + BN * 10 + MT with BN * 10 + MT as above (0 = automatic;
- *            additionally 1283 / 1284 = TF32 only, the generated operand kept in tensor memory instead of
- *            shared memory, tile 128 columns x 128 / 256 rows; never chosen automatically)
+ *            additionally, TF32 only, the generated operand kept in tensor memory instead of shared memory:
+ *            1283 / 1284 = tile of 128 columns x 128 / 256 rows, 1285 = 256 columns x 128 rows, which the
+ *            automatic choice uses where it would otherwise take 2561)
  *            and SPLIT the number of slices the contraction over (i, j) of every output tile is cut into, the
  *            counterpart of the reference's NUM_SPLITS and mode argument (triturus/lt2exp.py:533-541):
  *            0 = automatic (split when the output tiles would occupy fewer than half the SMs), 1 = never

@@ -10,7 +10,7 @@ from oracle import logspace_oracle as orc
 pytestmark = pytest.mark.gpu
 
 PRECISIONS = ["tf32", "3xtf32"]
-VARIANTS = [0, 1281, 1282, 2561, 2562, 1283, 1284]  # 1283 / 1284: generated operand in TMEM (TF32 only)
+VARIANTS = [0, 1281, 1282, 2561, 2562, 1283, 1284, 1285]  # 1283 / 1284: generated operand in TMEM (TF32 only)
 
 
 def _run(w, a, b, **kw):
@@ -66,12 +66,12 @@ SPLITS = [2, 3, 7, 16, 64, 9999]
 
 
 @pytest.mark.parametrize("split", SPLITS)
-@pytest.mark.parametrize("tile", [0, 1281, 2562, 1283, 1284])
+@pytest.mark.parametrize("tile", [0, 1281, 2562, 1283, 1284, 1285])
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_contraction_split(precision, tile, split):
     """Explicit slice counts on a ragged shape: I not divisible by the slice count, J not a multiple of the
     32-wide chunk, -inf entries and one all -inf column."""
-    if precision == "3xtf32" and tile in (2562, 1283, 1284):
+    if precision == "3xtf32" and tile in (2562, 1283, 1284, 1285):
         pytest.skip("no 256 x 256 tile and no TMEM-operand kernel in 3xTF32")
     g = torch.Generator().manual_seed(100 + split)
     R, S, I, J, K = 2, 150, 37, 70, 140
@@ -140,7 +140,7 @@ def test_unknown_mode_raises():
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_variants_on_ragged_shape(precision, variant):
-    if precision == "3xtf32" and variant in (1283, 1284):
+    if precision == "3xtf32" and variant in (1283, 1284, 1285):
         pytest.skip("the TMEM-operand kernel is TF32 only")
     g = torch.Generator().manual_seed(9)
     w = torch.rand(3, 270, 13, 37, generator=g)
@@ -242,7 +242,7 @@ def test_full_size_configs(name, batch, precision):
     tb.check_status()
 
 
-@pytest.mark.parametrize("variant", [1283, 1284])
+@pytest.mark.parametrize("variant", [1283, 1284, 1285])
 @pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1), (2, 129, 5, 1, 3), (2, 7, 9, 64, 257), (1, 300, 20, 31, 70),
                                    (3, 256, 16, 40, 384)])
 def test_tmem_operand_kernel_edge_shapes(shape, variant):

@@ -265,9 +265,10 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   if (tile_variant == 0) {
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
-    // (Not for 3xTF32 contractions longer than 1024: only the single-CTA kernel re-sums its accumulator
-    // in chunks, which keeps such sums within the 3xTF32 tolerance.)
-    const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 1024;
+    // (Not for 3xTF32 contractions longer than 4096, where the drift of the tensor core's truncating
+    // accumulator, ~1.2e-8 per term, would use up the 3xTF32 tolerance: only the single-CTA kernel re-sums
+    // its accumulator in chunks.)
+    const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool want_pair =
         stab_mode != 2 && !long_3x && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32, true);
@@ -543,6 +544,7 @@ static int launch_lt2exp_tmem(const CUtensorMap& tw, Lt2expParams p, int split_r
 //                              MT NS   (generated operand in TMEM, 128 columns k per tile, TF32)
 using LtM_1 = Lt2expTmemCfg<1, 8>;
 using LtM_2 = Lt2expTmemCfg<2, 6>;
+using LtM_1x2 = Lt2expTmemCfg<1, 4, 2>;  // 128 rows x two 128-column blocks sharing each w tile
 
 //                          BN   MT PREC NS NTW
 using LtT_128_1 = Lt2expCfg<128, 1, 0, 6, 8>;
@@ -556,14 +558,21 @@ using LtX_256_1 = Lt2expCfg<256, 1, 1, 2, 8>;
 }  // namespace tb200
 
 // Decodes SPLIT * 10000 + BN * 10 + MT, filling in the automatic tile shape.
-static int lt2exp_variant(int variant, int64_t R, int64_t S, int64_t K, int* bn, int* mt, int* split) {
+static int lt2exp_variant(int variant, int precision, int64_t R, int64_t S, int64_t K, int* bn, int* mt,
+                          int* split) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
   *split = variant / 10000;
   int tile = variant % 10000;
-  if (tile == 0) tile = tb200::auto_variant(R, S, K, true, false);
+  if (tile == 0) {
+    tile = tb200::auto_variant(R, S, K, true, false);
+    // 128 rows x 256 columns in TF32: the kernel that keeps the generated operand in TMEM moves a third of
+    // the shared-memory bytes per k-block (measured 8 % faster on such tiles).
+    if (tile == 2561 && precision == TRITURUS_B200_PRECISION_TF32) tile = 1285;
+  }
   *bn = tile / 10;
   *mt = tile % 10;
-  if (*bn == 128 && (*mt == 3 || *mt == 4)) return TRITURUS_B200_OK;  // operand in TMEM, 128 / 256 rows
+  // operand in TMEM: 128 columns x 128 / 256 rows (1283 / 1284), 256 columns x 128 rows (1285)
+  if (*bn == 128 && (*mt == 3 || *mt == 4 || *mt == 5)) return TRITURUS_B200_OK;
   if ((*bn != 128 && *bn != 256) || (*mt != 1 && *mt != 2)) return TRITURUS_B200_EINVAL;
   return TRITURUS_B200_OK;
 }
@@ -580,8 +589,9 @@ static int lt2exp_check_dims(int64_t R, int64_t S, int64_t I, int64_t J, int64_t
 template <class... Args>
 static int lt2exp_dispatch(int precision, int bn, int mt, Args... args) {
   using namespace tb200;
-  if (mt == 3 || mt == 4) {
+  if (mt == 3 || mt == 4 || mt == 5) {
     if (precision != TRITURUS_B200_PRECISION_TF32) return TRITURUS_B200_EINVAL;
+    if (mt == 5) return launch_lt2exp_tmem<LtM_1x2>(args...);
     return mt == 4 ? launch_lt2exp_tmem<LtM_2>(args...) : launch_lt2exp_tmem<LtM_1>(args...);
   }
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {
@@ -597,7 +607,7 @@ extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, in
   int rc = lt2exp_check_dims(R, S, I, J, K, precision);
   if (rc != TRITURUS_B200_OK) return rc;
   int bn, mt, split;
-  rc = lt2exp_variant(variant, R, S, K, &bn, &mt, &split);
+  rc = lt2exp_variant(variant, precision, R, S, K, &bn, &mt, &split);
   if (rc != TRITURUS_B200_OK) return rc;
   tb200::Lt2expParams p{};
   p.R = static_cast<int>(R);
@@ -639,7 +649,7 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
 
   int bn, mt, split;
   {
-    const int rc = lt2exp_variant(variant, R, S, K, &bn, &mt, &split);
+    const int rc = lt2exp_variant(variant, precision, R, S, K, &bn, &mt, &split);
     if (rc != TRITURUS_B200_OK) return rc;
   }
 

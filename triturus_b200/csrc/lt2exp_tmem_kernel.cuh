@@ -33,17 +33,20 @@
 
 namespace tb200 {
 
-template <int MT_, int NS_>
+template <int MT_, int NS_, int NB_ = 1>
 struct Lt2expTmemCfg {
   static constexpr int BM = 128, BK = 32;  // BM: rows s per w box
-  static constexpr int BN = 128;           // columns k per tile = TMEM lanes
+  static constexpr int NB = NB_;           // 128-column blocks per tile: each is one M = 128 MMA on the same w tile
+  static constexpr int BN = 128 * NB;      // columns k per tile
   static constexpr int MT = MT_, NS = NS_, PREC = 0, NTW = 8;
   static constexpr int W_TILE = BM * BK * 4;
   static constexpr int STAGE = MT * W_TILE;
-  static constexpr int ACC_COLS = MT * BM;
-  static constexpr int NBUF = (MT == 1) ? 2 : 1;
+  static constexpr int BLK_COLS = MT * BM;        // accumulator columns of one column block
+  static constexpr int ACC_COLS = NB * BLK_COLS;
+  static constexpr int P_STAGE = NB * BK;         // operand columns per stage
+  static constexpr int NBUF = (2 * ACC_COLS + NS * P_STAGE <= 512) ? 2 : 1;
   static constexpr int P_COL0 = NBUF * ACC_COLS;  // first operand column
-  static constexpr int TMEM_USED = P_COL0 + NS * BK;
+  static constexpr int TMEM_USED = P_COL0 + NS * P_STAGE;
   static constexpr int TMEM_COLS = 512;
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
@@ -54,7 +57,7 @@ struct Lt2expTmemCfg {
   static constexpr int NBAR = 3 * NS + 7;
   static constexpr int SMEM_BYTES = 1024 + NS * STAGE + 2 * BN * 4 + 2 * MPART * 4 + NBAR * 8 + 64;
   static_assert(TMEM_USED <= 512, "TMEM capacity");
-  static_assert(NGROUPS == 2, "two transform warps per TMEM lane quarter");
+  static_assert(NGROUPS * NB == 2, "eight transform warps: two groups on one column block, or one group on two");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
@@ -86,7 +89,7 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full[s], 5);  // the producer and the four warps (lane quarters) that write the operand stage
+      mbar_init(&full[s], 1 + Cfg::NTW / Cfg::NGROUPS);  // the producer and the warps that write the operand stage
       mbar_init(&opnd_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -163,7 +166,7 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
     // single thread issuing four MMAs per k-block after two fresh barrier round trips took ~790 cycles per
     // k-block against 512 cycles of tensor work.
     {
-      constexpr uint32_t idesc = umma_idesc_tf32(BN, BM * MT);  // M = 128 columns k, N = rows s
+      constexpr uint32_t idesc = umma_idesc_tf32(128, BM * MT);  // M = 128 columns k, N = rows s
       const uint32_t stage0 = smem_u32(stage_base);
       uint32_t tcount = 0;
       int s = 0;
@@ -188,10 +191,14 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
           tc_fence_after_sync();
           if (elect_one_sync()) {
             const uint64_t dw = umma_desc_k_sw128(stage0 + s * Cfg::STAGE);
-            const uint32_t pa = tmem_base + Cfg::P_COL0 + s * BK;
+            const uint32_t pa = tmem_base + Cfg::P_COL0 + s * Cfg::P_STAGE;
 #pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks)
-              umma_tf32_ts(d, pa + ks * 8, dw + 2 * ks, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            for (int blk = 0; blk < Cfg::NB; ++blk) {  // the column blocks share the w tile
+#pragma unroll
+              for (int ks = 0; ks < BK / 8; ++ks)
+                umma_tf32_ts(d + blk * Cfg::BLK_COLS, pa + blk * BK + ks * 8, dw + 2 * ks, idesc,
+                             (kb > 0 || ks > 0) ? 1u : 0u);
+            }
             umma_commit(&opnd_empty[s]);
           }
           ready = __all_sync(0xffffffffu, peek);
@@ -214,42 +221,47 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
       const int buf = tcount % Cfg::NBUF;
       const uint32_t aph = (tcount / Cfg::NBUF) & 1;
       const int slot = tcount & 1;
-      const int kcol = n0 + q * 32 + lane;
-      const bool col_ok = kcol < p.K;
-      float* out_col = p.out + static_cast<int64_t>(r) * p.out_s0 + kcol;
       if (!(ok = mbar_wait_warp(&acc_full[buf], aph, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
       tc_fence_after_sync();
-      const float m = msum[slot * BN + q * 32 + lane];
-      // One chunk = 32 rows s for this lane's column.  The loop stays rolled (two chunks per trip, the next
-      // one loading while the current one is finished): unrolled, every chunk was straight-line code run once
-      // per tile and the epilogue ran at instruction-fetch speed (2 000-10 000 cycles per chunk).
-      auto finish = [&](const uint32_t(&cur)[32], int sb) {
-        if (split_mode) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (col_ok && sb + e < p.S) atomicAdd(out_col + static_cast<int64_t>(sb + e) * p.out_s1, __uint_as_float(cur[e]));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float o = m + lg2_approx(__uint_as_float(cur[e])) * LN2_F;
-            if (col_ok && sb + e < p.S) out_col[static_cast<int64_t>(sb + e) * p.out_s1] = o;
-          }
-        }
-      };
-      const uint32_t acc0 = lane_base + buf * Cfg::ACC_COLS;
-      uint32_t v0[32], v1[32];
-      tmem_ld_32x32(acc0, v0);
 #pragma unroll 1
-      for (int c = 0; c < Cfg::ACC_COLS / 32; c += 2) {
-        const int sb = s0 + c * 32;
-        if (sb >= p.S) break;
+      for (int blk = 0; blk < Cfg::NB; ++blk) {  // column blocks of the tile: this lane's column in each
+        const int kcol = n0 + blk * 128 + q * 32 + lane;
+        const bool col_ok = kcol < p.K;
+        float* out_col = p.out + static_cast<int64_t>(r) * p.out_s0 + kcol;
+        const float m = msum[slot * BN + blk * 128 + q * 32 + lane];
+        // One chunk = 32 rows s for this lane's column.  The loop stays rolled (two chunks per trip, the
+        // next one loading while the current one is finished): unrolled, every chunk was straight-line code
+        // run once per tile and the epilogue ran at instruction-fetch speed (2 000-10 000 cycles per chunk).
+        auto finish = [&](const uint32_t(&cur)[32], int sb) {
+          if (split_mode) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col_ok && sb + e < p.S)
+                atomicAdd(out_col + static_cast<int64_t>(sb + e) * p.out_s1, __uint_as_float(cur[e]));
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float o = m + lg2_approx(__uint_as_float(cur[e])) * LN2_F;
+              if (col_ok && sb + e < p.S) out_col[static_cast<int64_t>(sb + e) * p.out_s1] = o;
+            }
+          }
+        };
+        const uint32_t acc0 = lane_base + buf * Cfg::ACC_COLS + blk * Cfg::BLK_COLS;
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(acc0, v0);
+#pragma unroll 1
+        for (int c = 0; c < Cfg::BLK_COLS / 32; c += 2) {
+          const int sb = s0 + c * 32;
+          if (sb >= p.S) break;
+          tmem_ld_wait();
+          tmem_ld_32x32(acc0 + (c + 1) * 32, v1);
+          finish(v0, sb);
+          tmem_ld_wait();
+          if (c + 2 < Cfg::BLK_COLS / 32) tmem_ld_32x32(acc0 + (c + 2) * 32, v0);
+          if (sb + 32 < p.S) finish(v1, sb + 32);
+        }
         tmem_ld_wait();
-        tmem_ld_32x32(acc0 + (c + 1) * 32, v1);
-        finish(v0, sb);
-        tmem_ld_wait();
-        if (c + 2 < Cfg::ACC_COLS / 32) tmem_ld_32x32(acc0 + (c + 2) * 32, v0);
-        if (sb + 32 < p.S) finish(v1, sb + 32);
       }
       tmem_ld_wait();
       tc_fence_before_sync();
@@ -265,7 +277,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
     const int n = tt % BN;   // column of the tile = TMEM lane owned by this thread
     const int grp = tt / BN; // this thread's group takes k-blocks with (i - i_lo) % 2 == grp
     constexpr int NG = Cfg::NGROUPS;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + Cfg::P_COL0;
+    // TMEM lane quarter of this warp; with two column blocks per tile the upper four warps write the second
+    // block's operand columns.
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + Cfg::P_COL0 +
+                               (Cfg::NB == 2 ? static_cast<uint32_t>((tt / 128) * BK) : 0u);
     uint32_t it = 0, tcount = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
@@ -350,7 +365,7 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
             for (int e = 0; e < 32; ++e) pv[e] = tf32_round_bits(ea * eb[e]);
             if (!(ok = mbar_wait_warp(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
             tc_fence_after_sync();
-            tmem_st_32x32(lane_base + s * BK, pv);
+            tmem_st_32x32(lane_base + s * Cfg::P_STAGE, pv);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
