@@ -84,30 +84,29 @@ struct Lt2expCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
-// Running maximum of four adjacent columns over rows first, first + step, ... < rows, eight 16-byte loads in
-// flight.  `quad` points at row 0 of the four columns.
+// Running maximum of four adjacent columns over rows first, first + step, ... < rows, sixteen 16-byte loads
+// in flight (the scan is a chain of memory round trips: fewer, wider rounds).  `quad` points at row 0 of the
+// four columns.
 __device__ __forceinline__ float4 quad_column_max(const float* quad, int64_t stride, int rows, int first, int step) {
   float4 m = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
   int i = first;
-  for (; i + 7 * step < rows; i += 8 * step) {
-    float4 v[8];
+  constexpr int INFLIGHT = 16;
+  const float4 ninf = m;
+  for (; i < rows; i += INFLIGHT * step) {
+    float4 v[INFLIGHT];
 #pragma unroll
-    for (int x = 0; x < 8; ++x)
-      v[x] = __ldg(reinterpret_cast<const float4*>(quad + static_cast<int64_t>(i + x * step) * stride));
+    for (int x = 0; x < INFLIGHT; ++x) {
+      const int row = i + x * step;
+      v[x] = ninf;  // rows past the end do not change the maximum
+      if (row < rows) v[x] = __ldg(reinterpret_cast<const float4*>(quad + static_cast<int64_t>(row) * stride));
+    }
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
+    for (int x = 0; x < INFLIGHT; ++x) {
       m.x = fmaxf(m.x, v[x].x);
       m.y = fmaxf(m.y, v[x].y);
       m.z = fmaxf(m.z, v[x].z);
       m.w = fmaxf(m.w, v[x].w);
     }
-  }
-  for (; i < rows; i += step) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(quad + static_cast<int64_t>(i) * stride));
-    m.x = fmaxf(m.x, v.x);
-    m.y = fmaxf(m.y, v.y);
-    m.z = fmaxf(m.z, v.z);
-    m.w = fmaxf(m.w, v.w);
   }
   return m;
 }
