@@ -474,6 +474,9 @@ static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
   if (request == 0 || request == 9999) {  // automatic; 9999: automatic, but at least two slices
     const int sms = sm_count();
     want = tiles * 2 > sms ? 1 : sms / tiles;
+    // Two more launches (zero-fill and log pass) cost about as much as 50 k-blocks of the main loop: a
+    // contraction shorter than that is left whole.
+    if (request == 0 && kb < 64) want = 1;
     if (request == 9999 && want < 2) want = 2;
   }
   if (want > kb / kMinSliceBlocks) want = kb / kMinSliceBlocks;
