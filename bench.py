@@ -39,7 +39,7 @@ from triturus_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 METRIC = "lm2exp/lt2exp effective TFLOP/s"
 
 
-def launches_per_step(wl, precision: str, variant: int) -> int:
+def launches_per_step(wl, precision: str, variant: int, chain: bool = False) -> int:
     """Kernels of this library launched per step, asked from the library: lm2exp is the contraction kernel
     plus, unless the max pass is fused into it, the stabiliser pre-pass; lt2exp is one kernel, or three
     (zero-fill, contraction slices, log pass) when the contraction is split over the SMs."""
@@ -49,6 +49,8 @@ def launches_per_step(wl, precision: str, variant: int) -> int:
     prec = 0 if precision == "tf32" else 1
     if wl.op == "lt2exp":
         n = _native.LIB.triturus_b200_lt2exp_launches(d["R"], d["S"], d["I"], d["J"], d["K"], prec, variant)
+    elif chain:
+        n = _native.LIB.triturus_b200_lm2exp_chain_launches(d["R"], d["I"], d["J"], d["K"], prec, variant, 1, 1)
     else:
         n = _native.LIB.triturus_b200_lm2exp_launches(d["R"], d["I"], d["J"], d["K"], prec, variant)
     if n <= 0:
@@ -280,6 +282,9 @@ def main() -> None:
     ap.add_argument("--profile-mode", action="store_true",
                     help="only W warm-up and K timed steps: no clock sampling, end-to-end leg or CPU baseline "
                          "(for runs under a profiler, whose printed numbers are never bench values)")
+    ap.add_argument("--chain", action="store_true",
+                    help="lm2exp workloads: time one inner link of a chain of layers (the stabiliser of b is "
+                         "supplied, the column maxima of the result are returned); not the headline configuration")
     ap.add_argument("--gather", action="store_true", help="also time an all-gather of the output shards (reported separately)")
     ap.add_argument("--sweep", choices=["lm2exp", "lt2exp"], default=None,
                     help="walk the reference's benchmark sweep for one op instead of the headline workload")
@@ -321,11 +326,18 @@ def main() -> None:
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
     step = make_step(wl.op, args.precision, args.variant)
+    if args.chain and wl.op != "lm2exp":
+        raise SystemExit("--chain applies to the lm2exp workloads")
 
     # Weak scaling: every rank owns one full batch of the workload (seeded per rank).
     host_inputs = [t.pin_memory() for t in make_inputs(wl, seed=rank)]
     inputs = [t.to(dev, non_blocking=True) for t in host_inputs]
     torch.cuda.synchronize()
+    if args.chain:
+        # Steady state of a chain: the previous layer's epilogue delivered the column maxima of b.
+        b_colmax = tb.colmax(inputs[1])
+        step = lambda a, b: tb.lm2exp(a, b, precision=args.precision, variant=args.variant,  # noqa: E731
+                                      b_colmax=b_colmax, return_colmax=True)[0]
 
     def barrier() -> None:
         if distributed:
@@ -436,9 +448,9 @@ def main() -> None:
 
     # lm2exp with a pre-pass launches two kernels per step; the roofline is that of the dominant one (the
     # contraction kernel), so the stabiliser pre-pass is timed on its own and taken off the step time.
-    n_launch = launches_per_step(wl, args.precision, args.variant)
+    n_launch = launches_per_step(wl, args.precision, args.variant, args.chain)
     prepass_ms = 0.0
-    if wl.op == "lm2exp" and n_launch == 2:
+    if wl.op == "lm2exp" and n_launch == 2 and not args.chain:
         for _ in range(3):
             tb.colmax(inputs[1])
         pe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -487,6 +499,7 @@ def main() -> None:
         roof["launch_ms"] = launch_ms
         roof["prepass_ms"] = prepass_ms
         roof["kernel"] = ("lt2exp_kernel" if wl.op == "lt2exp" else
+                          "lm2exp chain link (stabiliser supplied, column maxima returned)" if args.chain else
                           ("lm2exp_pair_kernel / lm2exp_kernel (step time minus the stabiliser pre-pass)" if n_launch == 2
                            else "lm2exp_kernel (fused max pass)"))
 
@@ -507,6 +520,7 @@ def main() -> None:
                 "workload": f"{wl.name}{' (custom dims)' if custom_dims else ''}: {wl.op} fp32 {wl.dims} per GPU",
                 "precision": args.precision,
                 "variant": args.variant,
+                **({"chain": "inner link: b_colmax supplied, out_colmax returned"} if args.chain else {}),
                 "sharding": f"batch r, one full batch per GPU x {world}",
                 "l2": (f"operands + result = {wl.bytes / 1e6:.0f} MB per step, larger than the 126 MB L2"
                        if flush is None else

@@ -70,6 +70,31 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
                              int32_t* status_dev, void* stream);
 
 /*
+ * lm2exp as one link of a chain of layers.  In a circuit the result of one layer is the log-space operand b
+ * of the next (the caller's loop around triturus/lm2exp.py:167; the reference recomputes the column maxima of
+ * every layer's input inside _ker_lm2exp, triturus/lm2exp.py:124-127).  Here the epilogue of layer n can
+ * hand layer n + 1 its stabiliser, so that no layer but the first scans its input for maxima:
+ *   b_colmax   (optional) [R,K] contiguous: max_j b[r,j,k], e.g. the out_colmax of the call that produced b,
+ *              or the output of triturus_b200_colmax_f32.  Values are clamped to +-1e38 when read.  When
+ *              given, no max pass of any kind runs and `workspace` may be NULL.  The result is only
+ *              meaningful if the values really are upper bounds close to the column maxima.
+ *   out_colmax (optional) [R,K] contiguous: receives max_i out[r,i,k], exactly the maximum of the values
+ *              written to out (-inf for a column that is entirely -inf).  The epilogue folds each block of
+ *              results into a per-CTA buffer and writes one value per tile column; when the tile has
+ *              several row tiles these are reductions into out_colmax, which one small fill launch sets
+ *              to -inf first (triturus_b200_lm2exp_chain_launches counts it).
+ * With both pointers NULL this is triturus_b200_lm2exp_f32.  variant codes 2xxxxx (fused max pass) are
+ * rejected together with b_colmax.
+ */
+int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant,
+                                        int have_b_colmax, int want_out_colmax);
+int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J,
+                                   int64_t K, const int64_t a_strides[3], const int64_t b_strides[3],
+                                   const int64_t out_strides[3], int precision, int variant, const float* b_colmax,
+                                   float* out_colmax, void* workspace, size_t workspace_bytes, int32_t* status_dev,
+                                   void* stream);
+
+/*
  * lt2exp: out[r,s,k] = log sum_{i,j} w[r,s,i,j] * exp(a[r,i,k]) * exp(b[r,j,k]), stabilised by the clamped
  * column maxima of a and b.
  * Replaces triturus/lt2exp.py:519-630 (host wrapper), :227-357 (_ker_lt2exp_unsplit) and :365-506

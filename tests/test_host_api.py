@@ -69,6 +69,15 @@ def test_argument_validation_returns_codes_without_a_gpu():
     assert rc == -1
     rc = lib.triturus_b200_lt2exp_f32(fake, fake, fake, fake, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 5, null, null)
     assert rc == -1  # unknown variant
+    # chain entry point: no workspace and no stabiliser; the same buffer for both sets of maxima; a fused
+    # max pass requested together with a supplied stabiliser
+    chain = lib.triturus_b200_lm2exp_chain_f32
+    rc = chain(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, null, null, null, 0, null, null)
+    assert rc == -3
+    rc = chain(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, fake, null, 0, null, null)
+    assert rc == -1
+    rc = chain(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 201281, fake, null, null, 0, null, null)
+    assert rc == -1
 
 
 def test_wrappers_keep_reference_assertions():
@@ -113,6 +122,18 @@ def test_precision_flag_mapping():
         resolve_precision("fp16")
 
 
+def test_chain_launch_counts():
+    """Kernels per call of the chain entry point: a supplied stabiliser removes the pre-pass (or turns the
+    fused max pass off), returned column maxima add one fill launch."""
+    f = _native.LIB.triturus_b200_lm2exp_chain_launches
+    assert f(32, 1024, 1024, 1024, 0, 0, 0, 0) == _native.LIB.triturus_b200_lm2exp_launches(32, 1024, 1024, 1024, 0, 0)
+    assert f(32, 1024, 1024, 1024, 0, 0, 1, 0) == 1
+    assert f(32, 1024, 1024, 1024, 0, 0, 1, 1) == 2
+    assert f(128, 256, 256, 8192, 0, 0, 0, 0) == 1  # fused max pass
+    assert f(128, 256, 256, 8192, 0, 0, 1, 1) == 1  # one row tile: maxima stored directly, no fill
+    assert f(32, 1024, 1024, 1024, 0, 202561, 1, 0) < 0
+
+
 def test_fake_kernels_infer_shapes():
     a = torch.empty(3, 5, 7, device="meta")
     b = torch.empty(3, 7, 9, device="meta")
@@ -120,6 +141,11 @@ def test_fake_kernels_infer_shapes():
     w = torch.empty(3, 4, 5, 7, device="meta")
     a = torch.empty(3, 5, 9, device="meta")
     assert torch.ops.triturus.lt2exp(w, a, b, 1, 0).shape == (3, 4, 9)
+    a = torch.empty(3, 5, 7, device="meta")
+    out, m = torch.ops.triturus.lm2exp_chain(a, b, None, True, 0, 0)
+    assert out.shape == (3, 5, 9) and m.shape == (3, 9)
+    out, m = torch.ops.triturus.lm2exp_chain(a, b, torch.empty(3, 9, device="meta"), False, 0, 0)
+    assert out.shape == (3, 5, 9) and m.numel() == 0
 
 
 def test_tma_ready_padding_rules():

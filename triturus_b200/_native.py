@@ -23,6 +23,8 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lm2exp_launches",
     "triturus_b200_lt2exp_launches",
     "triturus_b200_lm2exp_f32",
+    "triturus_b200_lm2exp_chain_launches",
+    "triturus_b200_lm2exp_chain_f32",
     "triturus_b200_lt2exp_f32",
     "triturus_b200_colmax_f32",
     "triturus_b200_lm2exp_static_max_columns",
@@ -81,6 +83,13 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.triturus_b200_lm2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
         c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_lm2exp_chain_launches.restype = c_int
+    lib.triturus_b200_lm2exp_chain_launches.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int]
+    lib.triturus_b200_lm2exp_chain_f32.restype = c_int
+    lib.triturus_b200_lm2exp_chain_f32.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
+        c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
     ]  # fmt: skip
     lib.triturus_b200_lt2exp_f32.restype = c_int
     lib.triturus_b200_lt2exp_f32.argtypes = [
@@ -240,6 +249,41 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     return out
 
 
+def _lm2exp_chain_impl(
+    a: torch.Tensor, b: torch.Tensor, b_colmax: torch.Tensor | None, want_colmax: bool, precision: int, variant: int
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """lm2exp as a link of a chain: takes the column maxima of b when the caller has them and can return
+    those of the result.  Returns (out, out_colmax); out_colmax is an empty tensor when not requested."""
+    _require_cuda(a, b)
+    R, I, J = a.shape
+    K = b.shape[2]
+    a = _tma_ready(a)
+    b = _tma_ready(b)
+    out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
+    out_colmax = torch.empty((R, K) if want_colmax else (0,), dtype=torch.float32, device=a.device)
+    if b_colmax is not None:
+        _require_cuda(b_colmax)
+        if b_colmax.shape != (R, K) or b_colmax.dtype != torch.float32 or b_colmax.device != b.device:
+            raise ValueError(f"b_colmax must be a float32 [{R}, {K}] tensor on {b.device}")
+        b_colmax = b_colmax.contiguous()
+        ws_ptr, ws_bytes, ws = None, 0, None
+    else:
+        ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
+        ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=a.device)
+        ws_ptr = ws.data_ptr()
+    with _on_device(a.device) as idx:
+        rc = LIB.triturus_b200_lm2exp_chain_f32(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K,
+            _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
+            int(precision), int(variant),
+            b_colmax.data_ptr() if b_colmax is not None else None,
+            out_colmax.data_ptr() if want_colmax else None,
+            ws_ptr, ws_bytes, _status_word(a.device).data_ptr(), _raw_stream(idx),
+        )  # fmt: skip
+    _check(rc, "triturus_b200_lm2exp_chain_f32")
+    return out, out_colmax
+
+
 def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
     _require_cuda(w, a, b)
     R, S, I, J = w.shape
@@ -264,6 +308,9 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
 
 lm2exp_op = torch.library.custom_op("triturus::lm2exp", _lm2exp_impl, mutates_args=(), device_types="cuda")
 lt2exp_op = torch.library.custom_op("triturus::lt2exp", _lt2exp_impl, mutates_args=(), device_types="cuda")
+lm2exp_chain_op = torch.library.custom_op(
+    "triturus::lm2exp_chain", _lm2exp_chain_impl, mutates_args=(), device_types="cuda"
+)
 
 
 def lm2exp_call(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
@@ -272,6 +319,12 @@ def lm2exp_call(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) 
     if torch.compiler.is_compiling():
         return lm2exp_op(a, b, precision, variant)
     return _lm2exp_impl(a, b, precision, variant)
+
+
+def lm2exp_chain_call(a, b, b_colmax, want_colmax: bool, precision: int, variant: int):
+    if torch.compiler.is_compiling():
+        return lm2exp_chain_op(a, b, b_colmax, want_colmax, precision, variant)
+    return _lm2exp_chain_impl(a, b, b_colmax, want_colmax, precision, variant)
 
 
 def lt2exp_call(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:
@@ -283,6 +336,12 @@ def lt2exp_call(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: in
 @lm2exp_op.register_fake
 def _lm2exp_fake(a, b, precision, variant):
     return a.new_empty((a.shape[0], a.shape[1], b.shape[2]))
+
+
+@lm2exp_chain_op.register_fake
+def _lm2exp_chain_fake(a, b, b_colmax, want_colmax, precision, variant):
+    out = a.new_empty((a.shape[0], a.shape[1], b.shape[2]))
+    return out, a.new_empty((a.shape[0], b.shape[2]) if want_colmax else (0,))
 
 
 @lt2exp_op.register_fake

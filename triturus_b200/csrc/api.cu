@@ -74,6 +74,11 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
   }
 }
 
+// Fills m[0..n) with -inf: the start value of the column maxima that an epilogue folds into it.
+__global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* __restrict__ m, int64_t n) {
+  for (int64_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) m[i] = -INFINITY;
+}
+
 // ----------------------------------------------------------------------------- driver entry point for tensor maps
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -255,13 +260,16 @@ struct Lm2expPlan {
   int bn, mt;   // output columns per tile, 128-row blocks per CTA
   bool pair;    // 256 x 256 tile on a pair of CTAs
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
+  bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
 };
 
-static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out) {
+// have_m: the caller supplies the stabiliser, so the tile is chosen as usual but no max pass of either kind runs.
+static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
+                       bool have_m = false) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
   const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
   int tile_variant = variant % 100000;
-  if (stab_mode > 2) return TRITURUS_B200_EINVAL;
+  if (stab_mode > 2 || (have_m && stab_mode == 2)) return TRITURUS_B200_EINVAL;
   if (tile_variant == 0) {
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
@@ -290,7 +298,8 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   out->bn = bn;
   out->mt = pair ? 4 : mt;
   out->pair = pair;
-  out->fused = fused;
+  out->fused = fused && !have_m;
+  out->colmax_exclusive = !pair && I <= 128 * mt;
   return TRITURUS_B200_OK;
 }
 
@@ -356,10 +365,12 @@ size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int
   return static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float);
 }
 
-int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
-                             const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
-                             int precision, int variant, void* workspace, size_t workspace_bytes,
-                             int32_t* status_dev, void* stream) {
+// Shared body of the lm2exp entry points.  b_colmax (optional): [R, K] column maxima of b supplied by the
+// caller, which replace the stabiliser pass.  out_colmax (optional): [R, K] receives max_i out[r, i, k].
+static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+                      const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                      int precision, int variant, const float* b_colmax, float* out_colmax, void* workspace,
+                      size_t workspace_bytes, int32_t* status_dev, void* stream) {
   if (a == nullptr || b == nullptr || out == nullptr || a_strides == nullptr || b_strides == nullptr ||
       out_strides == nullptr)
     return TRITURUS_B200_EINVAL;
@@ -367,9 +378,12 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   if (R > 65535 || I > (1 << 30) || J > (1 << 30) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
   if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
     return TRITURUS_B200_EINVAL;
-  if (workspace == nullptr || workspace_bytes < triturus_b200_lm2exp_workspace_bytes(R, I, J, K) ||
-      (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+  if (b_colmax == nullptr &&
+      (workspace == nullptr || workspace_bytes < triturus_b200_lm2exp_workspace_bytes(R, I, J, K) ||
+       (reinterpret_cast<uintptr_t>(workspace) & 255) != 0))
     return TRITURUS_B200_EWORKSPACE;
+  if (out_colmax != nullptr && (out_colmax == b_colmax || (reinterpret_cast<uintptr_t>(out_colmax) & 3) != 0))
+    return TRITURUS_B200_EINVAL;
 
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
   int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
@@ -383,18 +397,26 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
 
   Lm2expPlan plan;
   {
-    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
+    // A supplied stabiliser makes every max pass redundant (and a fused max pass cannot be requested as well).
+    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan, b_colmax != nullptr);
     if (prc != TRITURUS_B200_OK) return prc;
   }
   const int bn = plan.bn, mt = plan.mt;
   const bool pair = plan.pair, fused = plan.fused;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* m_ws = static_cast<float*>(workspace);
+  const float* m_ws = b_colmax != nullptr ? b_colmax : static_cast<const float*>(workspace);
   int rc = TRITURUS_B200_OK;
-  if (!fused) {
+  // Column maxima of the result: tiles of several row tiles reduce into the array, which therefore starts
+  // at -inf; a single row tile stores every column exactly once and needs no fill.
+  if (out_colmax != nullptr && !plan.colmax_exclusive) {
+    const int64_t n = R * K;
+    const int64_t blocks = (n + 255) / 256;
+    fill_neg_inf_kernel<<<static_cast<int>(blocks < 1184 ? blocks : 1184), 256, 0, st>>>(out_colmax, n);
+  }
+  if (!fused && b_colmax == nullptr) {
     const int64_t bstr[3] = {bs0, bs1, 1};
-    rc = triturus_b200_colmax_f32(b, m_ws, R, J, K, bstr, stream);
+    rc = triturus_b200_colmax_f32(b, static_cast<float*>(workspace), R, J, K, bstr, stream);
     if (rc != TRITURUS_B200_OK) return rc;
   }
 
@@ -432,6 +454,7 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   p.out_tma = out_tma ? 1 : 0;
   p.m_ws = m_ws;
   p.out = out;
+  p.out_max = out_colmax;
   p.out_s0 = os0;
   p.out_s1 = os1;
   p.R = static_cast<int>(R);
@@ -451,6 +474,34 @@ int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t
   }
   if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st);
   return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st);
+}
+
+int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+                             const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                             int precision, int variant, void* workspace, size_t workspace_bytes,
+                             int32_t* status_dev, void* stream) {
+  return lm2exp_run(a, b, out, R, I, J, K, a_strides, b_strides, out_strides, precision, variant, nullptr, nullptr,
+                    workspace, workspace_bytes, status_dev, stream);
+}
+
+int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J,
+                                   int64_t K, const int64_t a_strides[3], const int64_t b_strides[3],
+                                   const int64_t out_strides[3], int precision, int variant, const float* b_colmax,
+                                   float* out_colmax, void* workspace, size_t workspace_bytes, int32_t* status_dev,
+                                   void* stream) {
+  return lm2exp_run(a, b, out, R, I, J, K, a_strides, b_strides, out_strides, precision, variant, b_colmax,
+                    out_colmax, workspace, workspace_bytes, status_dev, stream);
+}
+
+int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant,
+                                        int have_b_colmax, int want_out_colmax) {
+  if (R <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  Lm2expPlan plan;
+  const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan, have_b_colmax != 0);
+  if (rc != TRITURUS_B200_OK) return rc;
+  return 1 + ((plan.fused || have_b_colmax) ? 0 : 1) + ((want_out_colmax && !plan.colmax_exclusive) ? 1 : 0);
 }
 
 }  // extern "C"

@@ -31,8 +31,10 @@
 namespace tb200 {
 
 struct Lm2expParams {
-  const float* m_ws;       // [R, K] clamped column maxima of b (read only when fused_max == 0)
+  const float* m_ws;       // [R, K] column maxima of b (read only when fused_max == 0; clamped on read)
   float* out;              // [R, I, K]
+  float* out_max;          // [R, K] receives max_i out[r,i,k], or nullptr; pre-filled with -inf by the
+                           // caller unless a single row tile covers I (then every column is stored once)
   int64_t out_s0, out_s1;  // element strides of out (innermost stride is 1)
   int R, I, J, K;
   int tiles_m, tiles_n, num_tiles;
@@ -72,8 +74,10 @@ struct Lm2expCfg {
   static constexpr int EPI_STAGE = 4 * 32 * 128;           // per epilogue warp one 32 x 32 fp32 box, 128B-swizzled
   static constexpr int MSUM_BYTES = 2 * BN * 4;
   static constexpr int MPART_BYTES = 2 * NTW * 32 * 4;
-  static constexpr int NBAR = 3 * NS + 7;
-  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + MSUM_BYTES + MPART_BYTES + NBAR * 8 + 64;
+  static constexpr int CMAX_BYTES = 2 * BN * 4;            // column maxima of the result, two tiles in flight
+  static constexpr int NBAR = 3 * NS + 8;
+  static constexpr int SMEM_BYTES =
+      1024 + NS * STAGE + EPI_STAGE + MSUM_BYTES + MPART_BYTES + CMAX_BYTES + NBAR * 8 + 64;
   static_assert(BN == 128 || BN == 256, "BN");
   static_assert(NTW % NGRP == 0 && ROWS_PER_WARP % 4 == 0, "transform warp mapping");
   static_assert(TMEM_USED <= 512, "TMEM capacity");
@@ -94,7 +98,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   uint8_t* epi_stage = smem + NS * Cfg::STAGE;                         // 4 warps x 4 KB, 1024-byte aligned
   float* msum = reinterpret_cast<float*>(epi_stage + Cfg::EPI_STAGE);  // [2][BN] stabiliser of the tile's columns
   float* mpart = msum + 2 * BN;                                        // [2][NTW][32] per-warp partial maxima
-  uint64_t* bars = reinterpret_cast<uint64_t*>(mpart + 2 * NTW * 32);
+  int* colbuf = reinterpret_cast<int*>(mpart + 2 * NTW * 32);         // [2][BN] see flush_tile_colmax
+  uint64_t* bars = reinterpret_cast<uint64_t*>(colbuf + 2 * BN);
   uint64_t* full = bars;                   // [NS] TMA bytes of the stage landed
   uint64_t* xf_done = bars + NS;           // [NS] transform warps finished with the stage
   uint64_t* stage_empty = bars + 2 * NS;   // [NS] stage may be overwritten
@@ -102,7 +107,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;      // [2] epilogue drained the buffer
   uint64_t* msum_empty = acc_empty + 2;    // [2] epilogue finished reading msum[slot]
   uint64_t* mx_bar = msum_empty + 2;       // [1] all transform warps published their partial maxima
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mx_bar + 1);
+  uint64_t* cm_bar = mx_bar + 1;           // [1] all epilogue warps folded their blocks of the tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -130,6 +136,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&msum_empty[s], 4);
     }
     mbar_init(mx_bar, NTW);
+    mbar_init(cm_bar, 4);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -139,6 +146,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  for (int c = threadIdx.x; c < 2 * BN; c += Cfg::NTHREADS) colbuf[c] = NEG_INF_BITS;
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -264,6 +272,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const bool use_tma = p.out_tma != 0;
     uint32_t tcount = 0, ccount = 0;
     bool ok = true;
+    const bool emit_max = p.out_max != nullptr;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       int r, n0, i0;
@@ -375,11 +384,25 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 }
               }
             }
+            if (emit_max) {
+              // the next layer's stabiliser: column maxima of this block of results, read back from the
+              // staging box when there is one (after the stores: the register form then reuses o's registers)
+              int* cb = colbuf + slot * BN + c * 32;
+              if (use_tma) fold_staged_colmax(stg, p.I - rbase, cb, lane);
+              else fold_block_colmax(o, rbase + lane < p.I, cb, lane);
+            }
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&msum_empty[slot]);
+      if (emit_max) {
+        // all four warps have folded their blocks of this tile: move its column maxima to global memory
+        if (lane == 0) mbar_arrive(cm_bar);
+        if (!(ok = mbar_wait_warp(cm_bar, tcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+        flush_tile_colmax(colbuf + slot * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0,
+                          p.tiles_m == 1, q * 32 + lane);
+      }
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
   } else if (warp >= 8) {
@@ -455,7 +478,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       } else {
         const float* mrow = p.m_ws + static_cast<int64_t>(r) * p.K;
 #pragma unroll
-        for (int x = 0; x < 4; ++x) m4[x] = (col0 + x < p.K) ? __ldg(mrow + col0 + x) : 0.f;
+        for (int x = 0; x < 4; ++x) m4[x] = (col0 + x < p.K) ? clamp_stab(__ldg(mrow + col0 + x)) : 0.f;
       }
 
       // publish the stabiliser of this tile's columns for the epilogue

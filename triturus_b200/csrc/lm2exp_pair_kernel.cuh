@@ -41,8 +41,9 @@ struct Lm2expPairCfg {
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int NTT = NTW * 32;
   static constexpr int EPI_STAGE = 4 * 32 * 128;
-  static constexpr int NBAR = 3 * NS + 4;
-  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + NBAR * 8 + 64;
+  static constexpr int CMAX_BYTES = 2 * BN * 4;  // column maxima of the result, two tiles in flight
+  static constexpr int NBAR = 3 * NS + 5;
+  static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + CMAX_BYTES + NBAR * 8 + 64;
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
 
@@ -57,13 +58,15 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
   uint8_t* epi_stage = smem + NS * Cfg::STAGE;  // 4 warps x 4 KB staging boxes, 1024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_STAGE);
+  int* colbuf = reinterpret_cast<int*>(epi_stage + Cfg::EPI_STAGE);  // [2][BN] see flush_tile_colmax
+  uint64_t* bars = reinterpret_cast<uint64_t*>(colbuf + 2 * BN);
   uint64_t* full = bars;                  // [NS] this CTA's TMA bytes landed
   uint64_t* xf_done = bars + NS;          // [NS] (leader's copy is used) transform warps of both CTAs done
   uint64_t* stage_empty = bars + 2 * NS;  // [NS] pair MMAs reading the stage retired (committed by the leader)
   uint64_t* acc_full = bars + 3 * NS;     // [2] accumulator buffer complete (committed by the leader)
   uint64_t* acc_empty = acc_full + 2;     // [2] (leader's copy is used) epilogues of both CTAs drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* cm_bar = acc_empty + 2;       // [1] this CTA's epilogue warps folded their blocks of the tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -88,6 +91,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 8);
     }
+    mbar_init(cm_bar, 4);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -97,6 +101,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish_pair();
   }
+  for (int c = threadIdx.x; c < 2 * BN; c += Cfg::NTHREADS) colbuf[c] = NEG_INF_BITS;
   // Both CTAs must have initialised their barriers before either one signals across.
   tc_fence_before_sync();
   cluster_sync_all();
@@ -192,8 +197,9 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int q = warp & 3;
     uint8_t* stg = epi_stage + q * 4096;
     const bool use_tma = p.out_tma != 0;
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, mcount = 0;  // tiles seen; tiles whose column maxima this CTA has written
     bool ok = true;
+    const bool emit_max = p.out_max != nullptr;
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
@@ -224,7 +230,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const int c = idx + h;
           if (c < nchunks) {
             const int k0 = n0 + c * 32;
-            const float m_lane = (k0 + lane < p.K) ? __ldg(mrow + k0 + lane) : 0.f;
+            const float m_lane = (k0 + lane < p.K) ? clamp_stab(__ldg(mrow + k0 + lane)) : 0.f;
             tmem_ld_wait();  // chunk c is in v[h]
             if (c + 1 < nchunks) {
               tmem_ld_32x32(tbase + (c + 1) * 32, v[h ^ 1]);
@@ -265,8 +271,24 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 }
               }
             }
+            if (emit_max) {
+              // the next layer's stabiliser: column maxima of this block of results (see lm2exp_kernel.cuh)
+              int* cb = colbuf + (mcount & 1) * BN + c * 32;
+              if (use_tma) fold_staged_colmax(stg, p.I - rbase, cb, lane);
+              else fold_block_colmax(o, rbase + lane < p.I, cb, lane);
+            }
           }
         }
+      }
+      if (emit_max) {
+        // The four warps of this CTA have folded their 128 rows; the other CTA of the pair and the other
+        // row tiles add theirs with the same reduction.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(cm_bar);
+        if (!(ok = mbar_wait_warp(cm_bar, mcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+        flush_tile_colmax(colbuf + (mcount & 1) * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0,
+                          false, q * 32 + lane);
+        ++mcount;
       }
     }
     if (use_tma && lane == 0) tma_store_wait_all();
@@ -290,7 +312,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
         colv[x] = col0 + x < p.K;
-        m4[x] = colv[x] ? __ldg(mrow + col0 + x) : 0.f;
+        m4[x] = colv[x] ? clamp_stab(__ldg(mrow + col0 + x)) : 0.f;
       }
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int s = it % NS;

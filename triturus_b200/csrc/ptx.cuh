@@ -431,6 +431,100 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float x, float y, flo
 
 __device__ __forceinline__ float clamp_stab(float m) { return fminf(fmaxf(m, -STAB_CLAMP), STAB_CLAMP); }
 
+// ----------------------------------------------------------------------------- column maxima of the result
+//
+// An epilogue that also returns m[k] = max_i out[i, k] folds every 32 x 32 block of results into a per-CTA
+// buffer in shared memory (one word per tile column, all four epilogue warps and all row blocks of the tile),
+// and writes the buffer to global memory once per tile.  Floats are kept as their bit patterns: non-negative
+// floats order like signed integers and negative floats in reverse like unsigned integers, so an integer
+// max / min does a float max whatever the sign of the stored value.  NaN does not occur.
+
+constexpr int NEG_INF_BITS = static_cast<int>(0xFF800000u);
+
+__device__ __forceinline__ void smem_max_f32(int* addr, float v) {
+  v += 0.f;  // -0 becomes +0, whose bit pattern orders correctly
+  if (v >= 0.f) atomicMax(addr, __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned*>(addr), __float_as_uint(v));
+}
+
+__device__ __forceinline__ void red_max_f32(float* addr, float v) {
+  v += 0.f;
+  if (v >= 0.f) {
+    asm volatile("red.global.max.s32 [%0], %1;" ::"l"(addr), "r"(__float_as_int(v)) : "memory");
+  } else {
+    asm volatile("red.global.min.u32 [%0], %1;" ::"l"(addr), "r"(__float_as_uint(v)) : "memory");
+  }
+}
+
+// Block held one row per lane (o[e] = column e of row `lane`) -> cb[0..31].  Transposing reduction: at
+// distance d a lane keeps the half of its columns whose index has bit d equal to its own lane bit and trades
+// the other half with lane ^ d, so after five rounds (16 + 8 + 4 + 2 + 1 shuffles) lane c holds the maximum
+// of column c over all 32 rows.
+__device__ __forceinline__ void fold_block_colmax(const float (&o)[32], bool row_valid, int* cb, int lane) {
+  float v[32];
+#pragma unroll
+  for (int e = 0; e < 32; ++e) v[e] = row_valid ? o[e] : -INFINITY;
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) {
+    const bool upper = (lane & d) != 0;
+#pragma unroll
+    for (int e = 0; e < d; ++e) {
+      const float keep = upper ? v[e + d] : v[e];
+      const float send = upper ? v[e] : v[e + d];
+      v[e] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, d));
+    }
+  }
+  smem_max_f32(cb + lane, v[0]);
+}
+
+// The same from the 32 x 32 staging box the epilogue has just written for its TMA store (row r at byte
+// r * 128, 16-byte chunk g at position g ^ (r % 8)): eight 16-byte loads give a lane 8 rows of 4 columns, which
+// it folds in registers; two shuffle rounds fold the four row slots of the warp.  A third of the instructions
+// of the register form.  The caller has synchronised the warp after the writes.
+__device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_valid, int* cb, int lane) {
+  const int g = lane & 7, rs = lane >> 3;
+  float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = rs + 4 * i;
+    const float4 v = *reinterpret_cast<const float4*>(stg + r * 128 + ((g ^ (r & 7)) << 4));
+    if (r < rows_valid) {
+      mx.x = fmaxf(mx.x, v.x);
+      mx.y = fmaxf(mx.y, v.y);
+      mx.z = fmaxf(mx.z, v.z);
+      mx.w = fmaxf(mx.w, v.w);
+    }
+  }
+#pragma unroll
+  for (int sh = 8; sh <= 16; sh <<= 1) {
+    mx.x = fmaxf(mx.x, __shfl_xor_sync(0xffffffffu, mx.x, sh));
+    mx.y = fmaxf(mx.y, __shfl_xor_sync(0xffffffffu, mx.y, sh));
+    mx.z = fmaxf(mx.z, __shfl_xor_sync(0xffffffffu, mx.z, sh));
+    mx.w = fmaxf(mx.w, __shfl_xor_sync(0xffffffffu, mx.w, sh));
+  }
+  if (rs == 0) {
+    smem_max_f32(cb + g * 4 + 0, mx.x);
+    smem_max_f32(cb + g * 4 + 1, mx.y);
+    smem_max_f32(cb + g * 4 + 2, mx.z);
+    smem_max_f32(cb + g * 4 + 3, mx.w);
+  }
+}
+
+// End of a tile, called by the four epilogue warps after they have met at a barrier: thread te of 128 moves
+// columns te, te + 128, ... of the tile's buffer to gcol (a plain store when this tile alone covers the
+// column, else a reduction with the other row tiles) and resets the buffer.
+__device__ __forceinline__ void flush_tile_colmax(int* cb, int bn, float* gcol, int ncols_valid, bool exclusive,
+                                                  int te) {
+  for (int c = te; c < bn; c += 128) {
+    const float v = __int_as_float(cb[c]);
+    cb[c] = NEG_INF_BITS;
+    if (c < ncols_valid) {
+      if (exclusive) gcol[c] = v;
+      else red_max_f32(gcol + c, v);
+    }
+  }
+}
+
 // Byte offset of element (row, col) inside a 128-byte-swizzled K-major tile (rows of 32 fp32).
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t col) {
   return row * 128u + ((((col >> 2) ^ (row & 7u)) << 4) | ((col & 3u) << 2));
