@@ -123,6 +123,23 @@ int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, flo
                              int32_t* status_dev, void* stream);
 
 /*
+ * lt2exp as one link of a chain of layers (see triturus_b200_lm2exp_chain_f32; the reference's kernels scan a
+ * and b for their column maxima in every call, triturus/lt2exp.py:305-311).
+ *   a_colmax, b_colmax (optional, both or neither) [R,K] contiguous: max_i a[r,i,k] and max_j b[r,j,k], e.g.
+ *              the out_colmax of the calls that produced a and b.  Clamped to +-1e38 when read; when given,
+ *              the kernels do not scan a and b.
+ *   out_colmax (optional) [R,K] contiguous: receives max_s out[r,s,k], exactly the maximum of the values
+ *              written to out; costs one small fill launch (one more than triturus_b200_lt2exp_launches
+ *              reports) and a reduction in the epilogue, or in the log pass of a split contraction.
+ * With all three NULL this is triturus_b200_lt2exp_f32.
+ */
+int triturus_b200_lt2exp_chain_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
+                                   int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
+                                   const int64_t a_strides[3], const int64_t b_strides[3],
+                                   const int64_t out_strides[3], int precision, int variant, const float* a_colmax,
+                                   const float* b_colmax, float* out_colmax, int32_t* status_dev, void* stream);
+
+/*
  * The stabiliser alone: m[r,k] = clamp(max_j x[r,j,k], -1e38, 1e38), m contiguous [R,K].
  * This is the pre-pass of triturus/lm2exp.py:125-127 (and baselines/lm2exp.py:11-12) as its own launch.
  */

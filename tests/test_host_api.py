@@ -78,6 +78,12 @@ def test_argument_validation_returns_codes_without_a_gpu():
     assert rc == -1
     rc = chain(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 201281, fake, null, null, 0, null, null)
     assert rc == -1
+    # lt2exp chain entry point: one set of maxima without the other; the same buffer in and out
+    ltc = lib.triturus_b200_lt2exp_chain_f32
+    rc = ltc(fake, fake, fake, fake, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 0, fake, null, null, null, null)
+    assert rc == -1
+    rc = ltc(fake, fake, fake, fake, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 0, fake, fake, fake, null, null)
+    assert rc == -1
 
 
 def test_wrappers_keep_reference_assertions():
@@ -146,6 +152,9 @@ def test_fake_kernels_infer_shapes():
     assert out.shape == (3, 5, 9) and m.shape == (3, 9)
     out, m = torch.ops.triturus.lm2exp_chain(a, b, torch.empty(3, 9, device="meta"), False, 0, 0)
     assert out.shape == (3, 5, 9) and m.numel() == 0
+    a = torch.empty(3, 5, 9, device="meta")
+    out, m = torch.ops.triturus.lt2exp_chain(w, a, b, None, None, True, 0, 0)
+    assert out.shape == (3, 4, 9) and m.shape == (3, 9)
 
 
 def test_tma_ready_padding_rules():

@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lm2exp_chain_launches",
     "triturus_b200_lm2exp_chain_f32",
     "triturus_b200_lt2exp_f32",
+    "triturus_b200_lt2exp_chain_f32",
     "triturus_b200_colmax_f32",
     "triturus_b200_lm2exp_static_max_columns",
     "triturus_b200_lm2exp_f32_static",
@@ -95,6 +96,11 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.triturus_b200_lt2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
         i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_lt2exp_chain_f32.restype = c_int
+    lib.triturus_b200_lt2exp_chain_f32.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+        i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]  # fmt: skip
     lib.triturus_b200_lm2exp_static_max_columns.restype = c_size_t
     lib.triturus_b200_lm2exp_static_max_columns.argtypes = []
@@ -302,6 +308,45 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
     return out
 
 
+def _colmax_arg(t: torch.Tensor | None, R: int, K: int, like: torch.Tensor, name: str) -> torch.Tensor | None:
+    if t is None:
+        return None
+    _require_cuda(t)
+    if t.shape != (R, K) or t.dtype != torch.float32 or t.device != like.device:
+        raise ValueError(f"{name} must be a float32 [{R}, {K}] tensor on {like.device}")
+    return t.contiguous()
+
+
+def _lt2exp_chain_impl(
+    w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, a_colmax: torch.Tensor | None,
+    b_colmax: torch.Tensor | None, want_colmax: bool, precision: int, variant: int,
+) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+    """lt2exp as a link of a chain: takes the column maxima of a and b when the caller has them and can
+    return those of the result.  Returns (out, out_colmax); out_colmax is empty when not requested."""
+    _require_cuda(w, a, b)
+    R, S, I, J = w.shape
+    K = a.shape[2]
+    w = _tma_ready(w)
+    a = _inner_contiguous(a)
+    b = _inner_contiguous(b)
+    a_colmax = _colmax_arg(a_colmax, R, K, a, "a_colmax")
+    b_colmax = _colmax_arg(b_colmax, R, K, a, "b_colmax")
+    out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)
+    out_colmax = torch.empty((R, K) if want_colmax else (0,), dtype=torch.float32, device=a.device)
+    with _on_device(a.device) as idx:
+        rc = LIB.triturus_b200_lt2exp_chain_f32(
+            w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), R, S, I, J, K,
+            _i64(w.stride()), _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
+            int(precision), int(variant),
+            a_colmax.data_ptr() if a_colmax is not None else None,
+            b_colmax.data_ptr() if b_colmax is not None else None,
+            out_colmax.data_ptr() if want_colmax else None,
+            _status_word(a.device).data_ptr(), _raw_stream(idx),
+        )  # fmt: skip
+    _check(rc, "triturus_b200_lt2exp_chain_f32")
+    return out, out_colmax
+
+
 # ---------------------------------------------------------------------------- torch custom ops
 # torch.ops.triturus.lm2exp / torch.ops.triturus.lt2exp: CUDA only, with shape-inferring fake kernels so
 # the ops trace under torch.compile / FakeTensor.  The reference defines no autograd for these ops.
@@ -325,6 +370,23 @@ def lm2exp_chain_call(a, b, b_colmax, want_colmax: bool, precision: int, variant
     if torch.compiler.is_compiling():
         return lm2exp_chain_op(a, b, b_colmax, want_colmax, precision, variant)
     return _lm2exp_chain_impl(a, b, b_colmax, want_colmax, precision, variant)
+
+
+lt2exp_chain_op = torch.library.custom_op(
+    "triturus::lt2exp_chain", _lt2exp_chain_impl, mutates_args=(), device_types="cuda"
+)
+
+
+def lt2exp_chain_call(w, a, b, a_colmax, b_colmax, want_colmax: bool, precision: int, variant: int):
+    if torch.compiler.is_compiling():
+        return lt2exp_chain_op(w, a, b, a_colmax, b_colmax, want_colmax, precision, variant)
+    return _lt2exp_chain_impl(w, a, b, a_colmax, b_colmax, want_colmax, precision, variant)
+
+
+@lt2exp_chain_op.register_fake
+def _lt2exp_chain_fake(w, a, b, a_colmax, b_colmax, want_colmax, precision, variant):
+    out = a.new_empty((w.shape[0], w.shape[1], a.shape[2]))
+    return out, a.new_empty((w.shape[0], a.shape[2]) if want_colmax else (0,))
 
 
 def lt2exp_call(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: int, variant: int) -> torch.Tensor:

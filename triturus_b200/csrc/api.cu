@@ -678,11 +678,16 @@ extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, in
   return rc == TRITURUS_B200_OK ? n : rc;
 }
 
-extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
-                                        int64_t S, int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
-                                        const int64_t a_strides[3], const int64_t b_strides[3],
-                                        const int64_t out_strides[3], int precision, int variant,
-                                        int32_t* status_dev, void* stream) {
+// Shared body of the lt2exp entry points.  a_colmax / b_colmax (optional, both or neither): [R, K] column
+// maxima of a and b, which replace the scan at the start of every tile.  out_colmax (optional): [R, K] receives
+// max_s out[r, s, k].
+static int lt2exp_run(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S, int64_t I,
+                      int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
+                      const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
+                      const float* a_colmax, const float* b_colmax, float* out_colmax, int32_t* status_dev,
+                      void* stream) {
+  if ((a_colmax == nullptr) != (b_colmax == nullptr)) return TRITURUS_B200_EINVAL;
+  if (out_colmax != nullptr && (out_colmax == a_colmax || out_colmax == b_colmax)) return TRITURUS_B200_EINVAL;
   if (w == nullptr || a == nullptr || b == nullptr || out == nullptr || w_strides == nullptr ||
       a_strides == nullptr || b_strides == nullptr || out_strides == nullptr)
     return TRITURUS_B200_EINVAL;
@@ -738,8 +743,37 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
   p.vec_ab = (K % 4 == 0 && aligned16(a) && aligned16(b) && as0 % 4 == 0 && as1 % 4 == 0 && bs0 % 4 == 0 &&
               bs1 % 4 == 0) ? 1 : 0;
   p.status = status_dev;
+  p.ma_in = a_colmax;
+  p.mb_in = b_colmax;
+  p.out_max = out_colmax;
+  if (out_colmax != nullptr) {
+    const int64_t n = R * K;
+    const int64_t blocks = (n + 255) / 256;
+    tb200::fill_neg_inf_kernel<<<static_cast<int>(blocks < 1184 ? blocks : 1184), 256, 0,
+                                 static_cast<cudaStream_t>(stream)>>>(out_colmax, n);
+  }
 
   return lt2exp_dispatch(precision, bn, mt, tw, p, split, static_cast<cudaStream_t>(stream), static_cast<int*>(nullptr));
+}
+
+extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
+                                        int64_t S, int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
+                                        const int64_t a_strides[3], const int64_t b_strides[3],
+                                        const int64_t out_strides[3], int precision, int variant,
+                                        int32_t* status_dev, void* stream) {
+  return lt2exp_run(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision, variant,
+                    nullptr, nullptr, nullptr, status_dev, stream);
+}
+
+extern "C" int triturus_b200_lt2exp_chain_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
+                                              int64_t S, int64_t I, int64_t J, int64_t K,
+                                              const int64_t w_strides[4], const int64_t a_strides[3],
+                                              const int64_t b_strides[3], const int64_t out_strides[3],
+                                              int precision, int variant, const float* a_colmax,
+                                              const float* b_colmax, float* out_colmax, int32_t* status_dev,
+                                              void* stream) {
+  return lt2exp_run(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision, variant,
+                    a_colmax, b_colmax, out_colmax, status_dev, stream);
 }
 
 // ----------------------------------------------------------------------------- lm2exp without caller scratch

@@ -50,6 +50,13 @@ struct Lt2expParams {
   int num_items;         // num_tiles * split_i * split_j
   int vec_ab;            // a and b allow 16-byte loads along k (alignment, strides and K multiples of 4)
   int* status;
+  // Chains of layers (all optional, contiguous [R, K]): column maxima of a and of b supplied by the caller
+  // (both or neither; clamped when read), which replace the scan of a and b; and max_s out[r,s,k], which the
+  // epilogue (or, for a split contraction, the log pass) folds into out_max, which the launcher fills with
+  // -inf first.
+  const float* ma_in;
+  const float* mb_in;
+  float* out_max;
 };
 
 template <int BN_, int MT_, int PREC_, int NS_, int NTW_>
@@ -377,6 +384,27 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
                 }
               }
             }
+            if (p.out_max != nullptr) {
+              // Column maxima of this 32 x 32 block for the next layer.  A tile of this kernel is hundreds of
+              // k-blocks long, so one reduction per block and warp straight into global memory is negligible.
+              float v2[32];
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v2[e] = row < p.S ? o[e] : -INFINITY;
+#pragma unroll
+              for (int d = 16; d >= 1; d >>= 1) {
+                const bool upper = (lane & d) != 0;
+#pragma unroll
+                for (int e = 0; e < d; ++e) {
+                  const float keep = upper ? v2[e + d] : v2[e];
+                  const float send = upper ? v2[e] : v2[e + d];
+                  v2[e] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, d));
+                }
+              }
+              if (k0 + lane < p.K) {
+                float* dst = p.out_max + static_cast<int64_t>(r) * p.K + k0 + lane;
+                red_max_f32(dst, v2[0]);
+              }
+            }
           }
         }
         if (Cfg::PROMOTE && !last) tmem_st_wait();
@@ -410,8 +438,10 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       // threads split the rows: with 16-byte loads a thread takes four adjacent columns and every RG-th row,
       // otherwise its own column and every NG-th row; partial maxima meet in shared memory.
       float* part = mpart + (tcount & 1) * Cfg::MPART;
-      int nparts;
-      if (p.vec_ab) {
+      int nparts = 0;
+      if (p.ma_in != nullptr) {
+        // the caller knows the maxima (a previous layer's epilogue produced them): no scan
+      } else if (p.vec_ab) {
         const int q = tt % Cfg::CQ, rg = tt / Cfg::CQ;
         float4 pa = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), pb = pa;
         if (n0 + 4 * q < p.K) {  // K is a multiple of 4 here: the quad is inside or outside as a whole
@@ -426,13 +456,20 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
         part[(Cfg::RG + grp) * BN + n] = col_ok ? strided_column_max(b_col, p.b_s1, p.J, grp, NG) : -INFINITY;
         nparts = NG;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(mx_bar);
-      if (!(ok = mbar_wait_warp(mx_bar, tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
       float ma = -INFINITY, mb = -INFINITY;
-      for (int g = 0; g < nparts; ++g) {
-        ma = fmaxf(ma, part[g * BN + n]);
-        mb = fmaxf(mb, part[(Cfg::RG + g) * BN + n]);
+      if (p.ma_in != nullptr) {
+        if (col_ok) {
+          ma = __ldg(p.ma_in + static_cast<int64_t>(r) * p.K + kcol);
+          mb = __ldg(p.mb_in + static_cast<int64_t>(r) * p.K + kcol);
+        }
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(mx_bar);
+        if (!(ok = mbar_wait_warp(mx_bar, tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        for (int g = 0; g < nparts; ++g) {
+          ma = fmaxf(ma, part[g * BN + n]);
+          mb = fmaxf(mb, part[(Cfg::RG + g) * BN + n]);
+        }
       }
       ma = clamp_stab(ma);
       mb = clamp_stab(mb);
@@ -567,8 +604,16 @@ __global__ void __launch_bounds__(256) lt2exp_finish_kernel(const Lt2expParams p
   const int k0 = blockIdx.x * 128;
   const int r = blockIdx.z;
   const int tid = threadIdx.x;
-  int nparts;
-  if (p.vec_ab) {
+  int nparts = 0;
+  if (p.ma_in != nullptr) {
+    if (tid < 128 && k0 + tid < p.K) {
+      part[0][0][tid] = __ldg(p.ma_in + static_cast<int64_t>(r) * p.K + k0 + tid);
+      part[1][0][tid] = __ldg(p.mb_in + static_cast<int64_t>(r) * p.K + k0 + tid);
+    } else if (tid < 128) {
+      part[0][0][tid] = part[1][0][tid] = -INFINITY;
+    }
+    nparts = 1;
+  } else if (p.vec_ab) {
     const int q = tid & 31, rg = tid >> 5;
     float4 pa = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), pb = pa;
     if (k0 + 4 * q < p.K) {
@@ -599,11 +644,15 @@ __global__ void __launch_bounds__(256) lt2exp_finish_kernel(const Lt2expParams p
   if (k0 + n >= p.K) return;
   const float m = msum[n];
   const int s_end = min(p.S, (static_cast<int>(blockIdx.y) + 1) * 64);
+  float cmx = -INFINITY;  // maximum of this thread's results: its column, every second row of the block
   for (int s = blockIdx.y * 64 + (tid >> 7); s < s_end; s += 2) {
     float* o = p.out + static_cast<int64_t>(r) * p.out_s0 + static_cast<int64_t>(s) * p.out_s1 + k0 + n;
     const float acc = *o;
-    *o = m + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
+    const float res = m + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
+    *o = res;
+    cmx = fmaxf(cmx, res);
   }
+  if (p.out_max != nullptr) red_max_f32(p.out_max + static_cast<int64_t>(r) * p.K + k0 + n, cmx);
 }
 
 }  // namespace tb200

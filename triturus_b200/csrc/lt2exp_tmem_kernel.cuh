@@ -229,6 +229,7 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
         const bool col_ok = kcol < p.K;
         float* out_col = p.out + static_cast<int64_t>(r) * p.out_s0 + kcol;
         const float m = msum[slot * BN + blk * 128 + q * 32 + lane];
+        float cmx = -INFINITY;  // running maximum of this lane's column over the rows of the tile
         // One chunk = 32 rows s for this lane's column.  The loop stays rolled (two chunks per trip, the
         // next one loading while the current one is finished): unrolled, every chunk was straight-line code
         // run once per tile and the epilogue ran at instruction-fetch speed (2 000-10 000 cycles per chunk).
@@ -243,7 +244,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const float o = m + lg2_approx(__uint_as_float(cur[e])) * LN2_F;
-              if (col_ok && sb + e < p.S) out_col[static_cast<int64_t>(sb + e) * p.out_s1] = o;
+              if (col_ok && sb + e < p.S) {
+                out_col[static_cast<int64_t>(sb + e) * p.out_s1] = o;
+                cmx = fmaxf(cmx, o);
+              }
             }
           }
         };
@@ -262,6 +266,12 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
           if (sb + 32 < p.S) finish(v1, sb + 32);
         }
         tmem_ld_wait();
+        if (p.out_max != nullptr && !split_mode && col_ok) {
+          // the next layer's stabiliser: this lane owns the column, so the maximum is a register
+          float* dst = p.out_max + static_cast<int64_t>(r) * p.K + kcol;
+          if (p.tiles_m == 1) *dst = cmx;
+          else red_max_f32(dst, cmx);
+        }
       }
       tmem_ld_wait();
       tc_fence_before_sync();
@@ -294,8 +304,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
 
       // Column maxima over the full I and J (see lt2exp_kernel.cuh).
       float* part = mpart + (tcount & 1) * Cfg::MPART;
-      int nparts;
-      if (p.vec_ab) {
+      int nparts = 0;
+      if (p.ma_in != nullptr) {
+        // maxima supplied by the caller: no scan
+      } else if (p.vec_ab) {
         const int q4 = tt % Cfg::CQ, rg = tt / Cfg::CQ;
         float4 pa = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY), pb = pa;
         if (n0 + 4 * q4 < p.K) {
@@ -310,13 +322,20 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
         part[(Cfg::RG + grp) * BN + n] = col_ok ? strided_column_max(b_col, p.b_s1, p.J, grp, NG) : -INFINITY;
         nparts = NG;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(mx_bar);
-      if (!(ok = mbar_wait_warp(mx_bar, tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
       float ma = -INFINITY, mb = -INFINITY;
-      for (int g = 0; g < nparts; ++g) {
-        ma = fmaxf(ma, part[g * BN + n]);
-        mb = fmaxf(mb, part[(Cfg::RG + g) * BN + n]);
+      if (p.ma_in != nullptr) {
+        if (col_ok) {
+          ma = __ldg(p.ma_in + static_cast<int64_t>(r) * p.K + kcol);
+          mb = __ldg(p.mb_in + static_cast<int64_t>(r) * p.K + kcol);
+        }
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(mx_bar);
+        if (!(ok = mbar_wait_warp(mx_bar, tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        for (int g = 0; g < nparts; ++g) {
+          ma = fmaxf(ma, part[g * BN + n]);
+          mb = fmaxf(mb, part[(Cfg::RG + g) * BN + n]);
+        }
       }
       ma = clamp_stab(ma);
       mb = clamp_stab(mb);

@@ -18,7 +18,10 @@ def lt2exp(
     mode: str = "auto",
     precision: str | None = None,
     variant: int = 0,
-) -> torch.Tensor:
+    a_colmax: torch.Tensor | None = None,
+    b_colmax: torch.Tensor | None = None,
+    return_colmax: bool = False,
+):
     """out[r,s,k] = log sum_{i,j} w[r,s,i,j] * exp(a[r,i,k]) * exp(b[r,j,k]) for fp32 CUDA tensors
     w [R,S,I,J], a [R,I,K], b [R,J,K].
 
@@ -30,6 +33,11 @@ def lt2exp(
     mode="split" always does, mode="auto" splits when the output tiles would occupy fewer than half the SMs
     (and never under torch.use_deterministic_algorithms(True), because the order of the reductions is not
     fixed).  `variant` = SPLIT * 10000 + BN * 10 + MT pins the slice count and the tile shape explicitly.
+
+    Chains of layers (no counterpart in the reference, whose kernels scan a and b for their column maxima in
+    every call, triturus/lt2exp.py:305-311): `a_colmax` / `b_colmax` (float32 [R,K], both or neither) are the
+    column maxima of `a` and `b` over their middle dimension, e.g. as returned by the calls that produced
+    them, and replace the scan; `return_colmax=True` returns `(out, m)` with `m[r,k] = max_s out[r,s,k]`.
     """
     assert len(w.shape) == 4
     assert len(a.shape) == len(b.shape) == 3
@@ -54,4 +62,9 @@ def lt2exp(
             variant += 10000
         elif mode == "split":
             variant += 9999 * 10000
-    return _native.lt2exp_call(w, a, b, prec, variant)
+    if a_colmax is None and b_colmax is None and not return_colmax:
+        return _native.lt2exp_call(w, a, b, prec, variant)
+    if (a_colmax is None) != (b_colmax is None):
+        raise ValueError("lt2exp: a_colmax and b_colmax must be given together")
+    out, m = _native.lt2exp_chain_call(w, a, b, a_colmax, b_colmax, bool(return_colmax), prec, variant)
+    return (out, m) if return_colmax else out
