@@ -193,3 +193,35 @@ def test_long_contraction_3xtf32(J, variant):
     assert torch.all(got[1, :, 3] == float("-inf"))
     res = orc.compare_logspace(got, want, ATOL["3xtf32"])
     assert res["ok"], res
+
+
+@pytest.mark.parametrize("variant", [0, 1281, 1282, 2561, 2562, 2564])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_transposed_a_is_read_in_place(precision, variant):
+    """a given as a transposed view (i contiguous, triturus/lm2exp.py:190-198 forwards any strides): the
+    kernels use it as an MN-major operand without a copy; results equal those of the contiguous copy."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(11)
+    R, I, J, K = 3, 300, 172, 530               # I a multiple of 4: the transposed view meets the TMA rules
+    a_t = torch.rand(R, J, I, generator=g)      # stored [R, J, I]
+    b = torch.randn(R, J, K, generator=g) * 5.0 + 100.0 * torch.randn(R, 1, K, generator=g)
+    a_view = a_t.cuda().transpose(1, 2)         # logical [R, I, J], stride 1 along i
+    assert _native._lm2exp_a_operand(a_view).data_ptr() == a_view.data_ptr()
+    got = tb.lm2exp(a_view, b.cuda(), precision=precision, variant=variant)
+    ref = tb.lm2exp(a_view.contiguous(), b.cuda(), precision=precision, variant=variant)
+    tb.check_status()
+    _assert_close(got.cpu(), a_t.transpose(1, 2).contiguous(), b, precision)
+    assert torch.equal(got, ref)                # same operand values in the same order
+
+
+def test_transposed_a_with_odd_rows_falls_back_to_a_copy():
+    import triturus_b200 as tb
+
+    g = torch.Generator().manual_seed(12)
+    a_t = torch.rand(2, 40, 131, generator=g)   # I = 131: the j stride of the view is not a multiple of 4
+    b = torch.randn(2, 40, 64, generator=g)
+    got = tb.lm2exp(a_t.cuda().transpose(1, 2), b.cuda(), precision="3xtf32")
+    tb.check_status()
+    _assert_close(got.cpu(), a_t.transpose(1, 2).contiguous(), b, "3xtf32")

@@ -189,6 +189,17 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return view
 
 
+def _lm2exp_a_operand(a: torch.Tensor) -> torch.Tensor:
+    """`a` [R,I,J] as the library takes it: unchanged when j is contiguous and the TMA rules hold, unchanged
+    too when it is a transposed view (i contiguous, the other strides multiples of 4 elements, base 16-byte
+    aligned), which the kernels read in place as an MN-major tensor-core operand; otherwise a padded copy."""
+    R, I, J = a.shape
+    if J > 1 and a.stride(2) != 1 and (I == 1 or a.stride(1) == 1) and a.data_ptr() % 16 == 0:
+        if a.stride(2) > 0 and a.stride(2) % 4 == 0 and (R == 1 or (a.stride(0) > 0 and a.stride(0) % 4 == 0)):
+            return a
+    return _tma_ready(a)
+
+
 def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
     """Return `t` or a contiguous copy when its innermost stride is not 1 or a stride is not positive."""
     if (t.shape[-1] == 1 or t.stride(-1) == 1) and all(
@@ -239,7 +250,7 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     _require_cuda(a, b)
     R, I, J = a.shape
     K = b.shape[2]
-    a = _tma_ready(a)
+    a = _lm2exp_a_operand(a)
     b = _tma_ready(b)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
@@ -263,7 +274,7 @@ def _lm2exp_chain_impl(
     _require_cuda(a, b)
     R, I, J = a.shape
     K = b.shape[2]
-    a = _tma_ready(a)
+    a = _lm2exp_a_operand(a)
     b = _tma_ready(b)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     out_colmax = torch.empty((R, K) if want_colmax else (0,), dtype=torch.float32, device=a.device)

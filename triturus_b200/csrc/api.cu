@@ -388,9 +388,17 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
   int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
   int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
-  if ((J > 1 && as2 != 1) || (K > 1 && bs2 != 1) || (K > 1 && os2 != 1)) return TRITURUS_B200_EALIGN;
+  if ((K > 1 && bs2 != 1) || (K > 1 && os2 != 1)) return TRITURUS_B200_EALIGN;
   if (!aligned16(a) || !aligned16(b)) return TRITURUS_B200_EALIGN;
-  if (!fix_stride(I, as1, round_up4(J)) || !fix_stride(R, as0, round_up4(J) * I)) return TRITURUS_B200_EALIGN;
+  // a with j contiguous is a K-major tensor-core operand; a transposed view (i contiguous) is used in place
+  // as an MN-major operand.
+  const bool a_mn = J > 1 && as2 != 1;
+  if (a_mn) {
+    if (I > 1 && as1 != 1) return TRITURUS_B200_EALIGN;
+    if (!fix_stride(J, as2, round_up4(I)) || !fix_stride(R, as0, round_up4(I) * J)) return TRITURUS_B200_EALIGN;
+  } else if (!fix_stride(I, as1, round_up4(J)) || !fix_stride(R, as0, round_up4(J) * I)) {
+    return TRITURUS_B200_EALIGN;
+  }
   if (!fix_stride(J, bs1, round_up4(K)) || !fix_stride(R, bs0, round_up4(K) * J)) return TRITURUS_B200_EALIGN;
   if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
   if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
@@ -421,7 +429,13 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
   }
 
   CUtensorMap ta, tb;
-  {
+  if (a_mn) {
+    const int64_t dims[3] = {I, J, R};
+    const int64_t strides[3] = {1, as2, as0};
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tmap(&ta, a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  } else {
     const int64_t dims[3] = {J, I, R};
     const int64_t strides[3] = {1, as1, as0};
     const uint32_t box[3] = {32, 128, 1};
@@ -452,6 +466,7 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
 
   Lm2expParams p;
   p.out_tma = out_tma ? 1 : 0;
+  p.a_mn = a_mn ? 1 : 0;
   p.m_ws = m_ws;
   p.out = out;
   p.out_max = out_colmax;

@@ -40,6 +40,8 @@ struct Lm2expParams {
   int tiles_m, tiles_n, num_tiles;
   int fused_max;
   int out_tma;              // out meets the TMA rules: the epilogue stores through tmap_out
+  int a_mn;                 // a is stored with i contiguous (a transposed view): MN-major A operand, loaded as
+                            // four 32 i x 32 j boxes per 128-row tile in the layout of the b boxes
   int* status;
 };
 
@@ -191,8 +193,17 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
             mbar_arrive_expect_tx(&full[s], (pass ? MT * Cfg::A_TILE : 0) + Cfg::B_TILE);
             if (pass) {
+              if (p.a_mn) {
 #pragma unroll
-              for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
+                for (int t = 0; t < MT; ++t) {
+#pragma unroll
+                  for (int g = 0; g < BM / 32; ++g)
+                    tma_load_3d(a_tile(s, 0, t) + g * 4096, &tmap_a, &full[s], i0 + t * BM + g * 32, kb * BK, r);
+                }
+              } else {
+#pragma unroll
+                for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
+              }
               if (prefetch_next) {
 #pragma unroll
                 for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
@@ -209,7 +220,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(BM, BN) | (1u << 16);  // B operand is MN-major
+      // B operand is MN-major; A too when a is a transposed view (bit 15)
+      const uint32_t idesc = umma_idesc_tf32(BM, BN) | (1u << 16) | (p.a_mn ? (1u << 15) : 0u);
+      const uint32_t a_step = p.a_mn ? 64u : 2u;  // encoded address step per 8 contraction values
       uint32_t it = 0, ccount = 0;  // k-block stages and accumulation chunks issued so far
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -242,19 +255,22 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
               const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
-              const uint64_t da_hi = umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
-              const uint64_t da_lo = PREC ? umma_desc_k_sw128(smem_u32(a_tile(s, 1, t))) : 0;
+              const uint64_t da_hi = p.a_mn ? umma_desc_mn_sw128_base32(smem_u32(a_tile(s, 0, t)), 4096)
+                                            : umma_desc_k_sw128(smem_u32(a_tile(s, 0, t)));
+              const uint64_t da_lo = !PREC ? 0
+                                     : p.a_mn ? umma_desc_mn_sw128_base32(smem_u32(a_tile(s, 1, t)), 4096)
+                                              : umma_desc_k_sw128(smem_u32(a_tile(s, 1, t)));
 #pragma unroll
               for (int ks = 0; ks < BK / 8; ++ks) {
                 // One MMA consumes 8 contraction values: 32 bytes along a K-major row of A, eight
                 // 128-byte rows (two 512-byte swizzle atoms) of the MN-major B boxes.
                 const uint32_t acc = (kb > kb0 || ks > 0) ? 1u : 0u;
                 if (PREC) {
-                  umma_tf32_ss(d, da_hi + 2 * ks, db_lo + 64 * ks, idesc, acc);
-                  umma_tf32_ss(d, da_lo + 2 * ks, db_hi + 64 * ks, idesc, 1u);
-                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_lo + 64 * ks, idesc, acc);
+                  umma_tf32_ss(d, da_lo + a_step * ks, db_hi + 64 * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, 1u);
                 } else {
-                  umma_tf32_ss(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, acc);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, acc);
                 }
               }
             }

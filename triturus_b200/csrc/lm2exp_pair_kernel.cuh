@@ -137,7 +137,13 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const uint32_t ph = (it / NS) & 1;
           if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
           mbar_arrive_expect_tx(&full[s], Cfg::A_TILE + Cfg::B_TILE);
-          tma_load_3d(a_tile(s, 0), &tmap_a, &full[s], kb * BK, my_i0, r);
+          if (p.a_mn) {
+#pragma unroll
+            for (int g = 0; g < BM / 32; ++g)
+              tma_load_3d(a_tile(s, 0) + g * 4096, &tmap_a, &full[s], my_i0 + g * 32, kb * BK, r);
+          } else {
+            tma_load_3d(a_tile(s, 0), &tmap_a, &full[s], kb * BK, my_i0, r);
+          }
 #pragma unroll
           for (int g = 0; g < NGRP; ++g)
             tma_load_3d(b_tile(s, 0) + g * Cfg::B_BOX, &tmap_b, &full[s], my_n0 + g * 32, kb * BK, r);
@@ -148,13 +154,17 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------------ pair MMA issuer (leader CTA only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_tf32(2 * BM, BN) | (1u << 16);  // M = 256 over the pair, B MN-major
+      // M = 256 over the pair, B MN-major; A MN-major too when a is a transposed view (bit 15)
+      const uint32_t idesc = umma_idesc_tf32(2 * BM, BN) | (1u << 16) | (p.a_mn ? (1u << 15) : 0u);
+      const uint32_t a_step = p.a_mn ? 64u : 2u;  // encoded address step per 8 contraction values
       // This one thread feeds both tensor cores, so its per-k-block overhead is kept minimal: descriptors
       // of stage 0 are built once (stage s adds s * STAGE / 16 to the encoded address), one barrier wait
       // (the transform warps waited for the TMA bytes before they arrived), one multicast commit.
       constexpr uint32_t STAGE_ENC = Cfg::STAGE >> 4;
-      const uint64_t da_hi0 = umma_desc_k_sw128(smem_u32(a_tile(0, 0)));
-      const uint64_t da_lo0 = umma_desc_k_sw128(smem_u32(a_tile(0, PREC ? 1 : 0)));
+      const uint64_t da_hi0 = p.a_mn ? umma_desc_mn_sw128_base32(smem_u32(a_tile(0, 0)), 4096)
+                                     : umma_desc_k_sw128(smem_u32(a_tile(0, 0)));
+      const uint64_t da_lo0 = p.a_mn ? umma_desc_mn_sw128_base32(smem_u32(a_tile(0, PREC ? 1 : 0)), 4096)
+                                     : umma_desc_k_sw128(smem_u32(a_tile(0, PREC ? 1 : 0)));
       const uint64_t db_hi0 = umma_desc_mn_sw128_base32(smem_u32(b_tile(0, 0)), Cfg::B_BOX);
       const uint64_t db_lo0 = umma_desc_mn_sw128_base32(smem_u32(b_tile(0, PREC ? 1 : 0)), Cfg::B_BOX);
       uint32_t s = 0, ph = 0, tcount = 0;
@@ -174,11 +184,11 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           for (int ks = 0; ks < BK / 8; ++ks) {
             const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
             if (PREC) {
-              umma_tf32_ss_pair(d, da_hi + 2 * ks, db_lo + 64 * ks, idesc, acc);
-              umma_tf32_ss_pair(d, da_lo + 2 * ks, db_hi + 64 * ks, idesc, 1u);
-              umma_tf32_ss_pair(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, 1u);
+              umma_tf32_ss_pair(d, da_hi + a_step * ks, db_lo + 64 * ks, idesc, acc);
+              umma_tf32_ss_pair(d, da_lo + a_step * ks, db_hi + 64 * ks, idesc, 1u);
+              umma_tf32_ss_pair(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, 1u);
             } else {
-              umma_tf32_ss_pair(d, da_hi + 2 * ks, db_hi + 64 * ks, idesc, acc);
+              umma_tf32_ss_pair(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, acc);
             }
           }
           // free the stage in both CTAs once these MMAs retire
