@@ -208,7 +208,7 @@ def test_transposed_a_is_read_in_place(precision, variant):
     a_t = torch.rand(R, J, I, generator=g)      # stored [R, J, I]
     b = torch.randn(R, J, K, generator=g) * 5.0 + 100.0 * torch.randn(R, 1, K, generator=g)
     a_view = a_t.cuda().transpose(1, 2)         # logical [R, I, J], stride 1 along i
-    assert _native._lm2exp_a_operand(a_view).data_ptr() == a_view.data_ptr()
+    assert _native._lm2exp_a_operand(a_view, K).data_ptr() == a_view.data_ptr()
     got = tb.lm2exp(a_view, b.cuda(), precision=precision, variant=variant)
     ref = tb.lm2exp(a_view.contiguous(), b.cuda(), precision=precision, variant=variant)
     tb.check_status()
