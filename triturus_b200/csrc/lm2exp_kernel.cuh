@@ -373,10 +373,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               o[g * 4 + 2] = m4.z + (PREC ? logf(a2) : lg2_approx(a2) * LN2_F);
               o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
             }
+            // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
+            // (16-byte chunk g at position g ^ (row % 8): conflict-free).
             if (use_tma) {
-              // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
-              // (16-byte chunk g at position g ^ (row % 8): conflict-free), then one lane hands the box to
-              // the TMA unit, which writes full rows and clips at the tensor's edges.
               if (lane == 0) tma_store_wait_read<0>();  // the previous box has been read out
               __syncwarp();
 #pragma unroll
@@ -384,6 +383,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
                     make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              // one lane hands the box to the TMA unit, which writes full rows and clips at the tensor's edges
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
@@ -391,21 +391,24 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 tma_store_commit();
               }
             } else {
-              const int row = rbase + lane;
-              if (row < p.I) {
-                float* out_row = out_r + static_cast<int64_t>(row) * p.out_s1;
+              // The result does not meet the TMA rules (K not a multiple of 4, unaligned base): the warp
+              // writes the box row by row, 32 consecutive floats per store instruction.
+              __syncwarp();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                  if (k0 + e < p.K) out_row[k0 + e] = o[e];
-                }
+              for (int g = 0; g < 8; ++g) {
+                *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
+                    make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              __syncwarp();
+              if (k0 + lane < p.K)
+                store_staged_rows(stg, out_r + static_cast<int64_t>(rbase) * p.out_s1 + k0 + lane, p.out_s1,
+                                  min(32, p.I - rbase), lane);
             }
             if (emit_max) {
               // the next layer's stabiliser: column maxima of this block of results, read back from the
-              // staging box when there is one (after the stores: the register form then reuses o's registers)
+              // staging box
               int* cb = colbuf + slot * BN + c * 32;
-              if (use_tma) fold_staged_colmax(stg, p.I - rbase, cb, lane);
-              else fold_block_colmax(o, rbase + lane < p.I, cb, lane);
+              fold_staged_colmax(stg, p.I - rbase, cb, lane);
             }
           }
         }

@@ -256,15 +256,16 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               const float acc = __uint_as_float(v[h][e]);
               o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
             }
+            // swizzled 32 x 32 staging box, then TMA store or row-wise stores (see lm2exp_kernel.cuh)
             if (use_tma) {
-              // swizzled 32 x 32 staging box -> TMA store (see lm2exp_kernel.cuh)
-              if (lane == 0) tma_store_wait_read<0>();
+              if (lane == 0) tma_store_wait_read<0>();  // the previous box has been read out
               __syncwarp();
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
                     make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              // one lane hands the box to the TMA unit, which writes full rows and clips at the tensor's edges
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
@@ -272,20 +273,23 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 tma_store_commit();
               }
             } else {
-              const int row = rbase + lane;
-              if (row < p.I) {
-                float* out_row = out_r + static_cast<int64_t>(row) * p.out_s1;
+              // The result does not meet the TMA rules (K not a multiple of 4, unaligned base): the warp
+              // writes the box row by row, 32 consecutive floats per store instruction.
+              __syncwarp();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                  if (k0 + e < p.K) out_row[k0 + e] = o[e];
-                }
+              for (int g = 0; g < 8; ++g) {
+                *reinterpret_cast<float4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) =
+                    make_float4(o[g * 4], o[g * 4 + 1], o[g * 4 + 2], o[g * 4 + 3]);
               }
+              __syncwarp();
+              if (k0 + lane < p.K)
+                store_staged_rows(stg, out_r + static_cast<int64_t>(rbase) * p.out_s1 + k0 + lane, p.out_s1,
+                                  min(32, p.I - rbase), lane);
             }
             if (emit_max) {
               // the next layer's stabiliser: column maxima of this block of results (see lm2exp_kernel.cuh)
               int* cb = colbuf + (mcount & 1) * BN + c * 32;
-              if (use_tma) fold_staged_colmax(stg, p.I - rbase, cb, lane);
-              else fold_block_colmax(o, rbase + lane < p.I, cb, lane);
+              fold_staged_colmax(stg, p.I - rbase, cb, lane);
             }
           }
         }

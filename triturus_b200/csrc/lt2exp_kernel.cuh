@@ -387,23 +387,8 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
             if (p.out_max != nullptr) {
               // Column maxima of this 32 x 32 block for the next layer.  A tile of this kernel is hundreds of
               // k-blocks long, so one reduction per block and warp straight into global memory is negligible.
-              float v2[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) v2[e] = row < p.S ? o[e] : -INFINITY;
-#pragma unroll
-              for (int d = 16; d >= 1; d >>= 1) {
-                const bool upper = (lane & d) != 0;
-#pragma unroll
-                for (int e = 0; e < d; ++e) {
-                  const float keep = upper ? v2[e + d] : v2[e];
-                  const float send = upper ? v2[e] : v2[e + d];
-                  v2[e] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, d));
-                }
-              }
-              if (k0 + lane < p.K) {
-                float* dst = p.out_max + static_cast<int64_t>(r) * p.K + k0 + lane;
-                red_max_f32(dst, v2[0]);
-              }
+              const float cmx = block_colmax_to_lanes(o, row < p.S, lane);
+              if (k0 + lane < p.K) red_max_f32(p.out_max + static_cast<int64_t>(r) * p.K + k0 + lane, cmx);
             }
           }
         }

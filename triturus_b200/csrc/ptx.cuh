@@ -456,11 +456,11 @@ __device__ __forceinline__ void red_max_f32(float* addr, float v) {
   }
 }
 
-// Block held one row per lane (o[e] = column e of row `lane`) -> cb[0..31].  Transposing reduction: at
-// distance d a lane keeps the half of its columns whose index has bit d equal to its own lane bit and trades
-// the other half with lane ^ d, so after five rounds (16 + 8 + 4 + 2 + 1 shuffles) lane c holds the maximum
-// of column c over all 32 rows.
-__device__ __forceinline__ void fold_block_colmax(const float (&o)[32], bool row_valid, int* cb, int lane) {
+// Block held one row per lane (o[e] = column e of row `lane`): returns in lane c the maximum of column c over
+// the rows with row_valid.  Transposing reduction: at distance d a lane keeps the half of its columns whose
+// index has bit d equal to its own lane bit and trades the other half with lane ^ d, so five rounds
+// (16 + 8 + 4 + 2 + 1 shuffles) do it.
+__device__ __forceinline__ float block_colmax_to_lanes(const float (&o)[32], bool row_valid, int lane) {
   float v[32];
 #pragma unroll
   for (int e = 0; e < 32; ++e) v[e] = row_valid ? o[e] : -INFINITY;
@@ -474,13 +474,13 @@ __device__ __forceinline__ void fold_block_colmax(const float (&o)[32], bool row
       v[e] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, d));
     }
   }
-  smem_max_f32(cb + lane, v[0]);
+  return v[0];
 }
 
 // The same from the 32 x 32 staging box the epilogue has just written for its TMA store (row r at byte
 // r * 128, 16-byte chunk g at position g ^ (r % 8)): eight 16-byte loads give a lane 8 rows of 4 columns, which
 // it folds in registers; two shuffle rounds fold the four row slots of the warp.  A third of the instructions
-// of the register form.  The caller has synchronised the warp after the writes.
+// of block_colmax_to_lanes.  The caller has synchronised the warp after the writes.
 __device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_valid, int* cb, int lane) {
   const int g = lane & 7, rs = lane >> 3;
   float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
@@ -507,6 +507,21 @@ __device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_
     smem_max_f32(cb + g * 4 + 1, mx.y);
     smem_max_f32(cb + g * 4 + 2, mx.z);
     smem_max_f32(cb + g * 4 + 3, mx.w);
+  }
+}
+
+// Rows 0..nrows-1 of a staged 32 x 32 box to global memory, lane = column: every store instruction of the
+// warp writes 32 consecutive floats of one row (`dst` points at this lane's column of row 0).  For results
+// that cannot go through a TMA store.  Kept out of line: inlined, its address arithmetic competes for
+// registers with the accumulator chunks the epilogue holds.
+__device__ __noinline__ void store_staged_rows(const uint8_t* stg, float* dst, int64_t row_stride, int nrows,
+                                               int lane) {
+  const uint8_t* src = stg + (lane & 3) * 4;
+#pragma unroll 4
+  for (int rr = 0; rr < 32; ++rr) {
+    if (rr < nrows)
+      dst[static_cast<int64_t>(rr) * row_stride] =
+          *reinterpret_cast<const float*>(src + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4));
   }
 }
 
