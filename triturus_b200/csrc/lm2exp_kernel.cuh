@@ -77,7 +77,7 @@ struct Lm2expCfg {
   static constexpr int MSUM_BYTES = 2 * BN * 4;
   static constexpr int MPART_BYTES = 2 * NTW * 32 * 4;
   static constexpr int CMAX_BYTES = 2 * BN * 4;            // column maxima of the result, two tiles in flight
-  static constexpr int NBAR = 3 * NS + 8;
+  static constexpr int NBAR = 3 * NS + 16;
   static constexpr int SMEM_BYTES =
       1024 + NS * STAGE + EPI_STAGE + MSUM_BYTES + MPART_BYTES + CMAX_BYTES + NBAR * 8 + 64;
   static_assert(BN == 128 || BN == 256, "BN");
@@ -109,8 +109,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;      // [2] epilogue drained the buffer
   uint64_t* msum_empty = acc_empty + 2;    // [2] epilogue finished reading msum[slot]
   uint64_t* mx_bar = msum_empty + 2;       // [1] all transform warps published their partial maxima
-  uint64_t* cm_bar = mx_bar + 1;           // [1] all epilogue warps folded their blocks of the tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 1);
+  uint64_t* cm_bar = mx_bar + 1;           // [1] both fold warps folded their blocks of the tile
+  uint64_t* box_ready = cm_bar + 1;        // [4] epilogue warp q filled its staging box
+  uint64_t* box_free = box_ready + 4;      // [4] the fold warp has read epilogue warp q's staging box
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(box_free + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -138,7 +140,11 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&msum_empty[s], 4);
     }
     mbar_init(mx_bar, NTW);
-    mbar_init(cm_bar, 4);
+    mbar_init(cm_bar, 2);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&box_ready[s], 1);
+      mbar_init(&box_free[s], 1);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -287,6 +293,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* stg = epi_stage + q * 4096;  // this warp's staging box
     const bool use_tma = p.out_tma != 0;
     uint32_t tcount = 0, ccount = 0;
+    uint32_t nblk = 0;  // staging boxes handed to the fold warp so far
     bool ok = true;
     const bool emit_max = p.out_max != nullptr;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -343,7 +350,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       uint32_t v[2][32];
       tmem_ld_32x32(tbase, v[0]);
 #pragma unroll 1
-      for (int idx = 0; idx < nchunks; idx += 2) {
+      for (int idx = 0; ok && idx < nchunks; idx += 2) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int cur = idx + h;
@@ -375,6 +382,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
             // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
             // (16-byte chunk g at position g ^ (row % 8): conflict-free).
+            // the fold warp (column maxima of the result) has read the previous box
+            if (emit_max && nblk > 0 &&
+                !(ok = mbar_wait_warp(&box_free[q], (nblk - 1) & 1, ctl, STATUS_TIMEOUT_EPILOGUE)))
+              break;
             if (use_tma) {
               if (lane == 0) tma_store_wait_read<0>();  // the previous box has been read out
               __syncwarp();
@@ -405,25 +416,52 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                                   min(32, p.I - rbase), lane);
             }
             if (emit_max) {
-              // the next layer's stabiliser: column maxima of this block of results, read back from the
-              // staging box
-              int* cb = colbuf + slot * BN + c * 32;
-              fold_staged_colmax(stg, p.I - rbase, cb, lane);
+              // The next layer's stabiliser: the box goes to this warp's fold warp, which takes the column
+              // maxima of the block off this warp's critical path.
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&box_ready[q]);
+              ++nblk;
             }
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&msum_empty[slot]);
-      if (emit_max) {
-        // all four warps have folded their blocks of this tile: move its column maxima to global memory
-        if (lane == 0) mbar_arrive(cm_bar);
-        if (!(ok = mbar_wait_warp(cm_bar, tcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
-        flush_tile_colmax(colbuf + slot * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0,
-                          p.tiles_m == 1, q * 32 + lane);
-      }
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
+  } else if (warp >= 2 && warp < 4 && p.out_max != nullptr) {
+    // ------------------------------------------------------------------ fold: column maxima of the result
+    // Warp 2 serves epilogue warps 4 and 5, warp 3 serves 6 and 7: it reads each staged 32 x 32 block of
+    // results, hands the box back as soon as it holds it in registers, and folds the column maxima into the
+    // tile's buffer; at the end of a tile the two fold warps write one value per column to global memory.
+    const int fw = warp - 2;
+    uint32_t nb[2] = {0, 0};
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      int r, n0, i0;
+      decode(tile, r, n0, i0);
+      const int slot = tcount & 1;
+      const int nt = min(MT, (p.I - i0 + BM - 1) / BM);
+      const int nc = min(BN / 32, (p.K - n0 + 31) / 32);
+      for (int cur = 0; ok && cur < nt * nc; ++cur) {  // the epilogue's block order
+        const int t = cur / nc, c = cur - t * nc;
+#pragma unroll
+        for (int qq = 0; qq < 2; ++qq) {
+          const int q = 2 * fw + qq;
+          if (!(ok = mbar_wait_warp(&box_ready[q], nb[qq] & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+          ++nb[qq];
+          fold_staged_colmax(epi_stage + q * 4096, p.I - (i0 + t * BM + q * 32), colbuf + slot * BN + c * 32, lane,
+                             &box_free[q]);
+        }
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cm_bar);
+      if (!(ok = mbar_wait_warp(cm_bar, tcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+      flush_tile_colmax(colbuf + slot * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0,
+                        p.tiles_m == 1, fw * 32 + lane);
+    }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: b boxes -> E operand, in place
     const int wv = warp - 8;

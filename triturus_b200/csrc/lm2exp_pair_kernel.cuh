@@ -42,7 +42,7 @@ struct Lm2expPairCfg {
   static constexpr int NTT = NTW * 32;
   static constexpr int EPI_STAGE = 4 * 32 * 128;
   static constexpr int CMAX_BYTES = 2 * BN * 4;  // column maxima of the result, two tiles in flight
-  static constexpr int NBAR = 3 * NS + 5;
+  static constexpr int NBAR = 3 * NS + 13;
   static constexpr int SMEM_BYTES = 1024 + NS * STAGE + EPI_STAGE + CMAX_BYTES + NBAR * 8 + 64;
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
@@ -65,8 +65,10 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   uint64_t* stage_empty = bars + 2 * NS;  // [NS] pair MMAs reading the stage retired (committed by the leader)
   uint64_t* acc_full = bars + 3 * NS;     // [2] accumulator buffer complete (committed by the leader)
   uint64_t* acc_empty = acc_full + 2;     // [2] (leader's copy is used) epilogues of both CTAs drained it
-  uint64_t* cm_bar = acc_empty + 2;       // [1] this CTA's epilogue warps folded their blocks of the tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cm_bar + 1);
+  uint64_t* cm_bar = acc_empty + 2;       // [1] this CTA's two fold warps folded their blocks of the tile
+  uint64_t* box_ready = cm_bar + 1;       // [4] epilogue warp q filled its staging box
+  uint64_t* box_free = box_ready + 4;     // [4] the fold warp has read epilogue warp q's staging box
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(box_free + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -91,7 +93,11 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 8);
     }
-    mbar_init(cm_bar, 4);
+    mbar_init(cm_bar, 2);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&box_ready[s], 1);
+      mbar_init(&box_free[s], 1);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -207,7 +213,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int q = warp & 3;
     uint8_t* stg = epi_stage + q * 4096;
     const bool use_tma = p.out_tma != 0;
-    uint32_t tcount = 0, mcount = 0;  // tiles seen; tiles whose column maxima this CTA has written
+    uint32_t tcount = 0, nblk = 0;  // tiles seen; staging boxes handed to the fold warp so far
     bool ok = true;
     const bool emit_max = p.out_max != nullptr;
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
@@ -234,7 +240,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       uint32_t v[2][32];
       tmem_ld_32x32(tbase, v[0]);
 #pragma unroll 1
-      for (int idx = 0; idx < nchunks; idx += 2) {
+      for (int idx = 0; ok && idx < nchunks; idx += 2) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int c = idx + h;
@@ -257,6 +263,10 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
             }
             // swizzled 32 x 32 staging box, then TMA store or row-wise stores (see lm2exp_kernel.cuh)
+            // the fold warp (column maxima of the result) has read the previous box
+            if (emit_max && nblk > 0 &&
+                !(ok = mbar_wait_warp(&box_free[q], (nblk - 1) & 1, ctl, STATUS_TIMEOUT_EPILOGUE)))
+              break;
             if (use_tma) {
               if (lane == 0) tma_store_wait_read<0>();  // the previous box has been read out
               __syncwarp();
@@ -287,25 +297,49 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                                   min(32, p.I - rbase), lane);
             }
             if (emit_max) {
-              // the next layer's stabiliser: column maxima of this block of results (see lm2exp_kernel.cuh)
-              int* cb = colbuf + (mcount & 1) * BN + c * 32;
-              fold_staged_colmax(stg, p.I - rbase, cb, lane);
+              // the next layer's stabiliser: the box goes to this warp's fold warp (see lm2exp_kernel.cuh)
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&box_ready[q]);
+              ++nblk;
             }
           }
         }
       }
-      if (emit_max) {
-        // The four warps of this CTA have folded their 128 rows; the other CTA of the pair and the other
-        // row tiles add theirs with the same reduction.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(cm_bar);
-        if (!(ok = mbar_wait_warp(cm_bar, mcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
-        flush_tile_colmax(colbuf + (mcount & 1) * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0,
-                          false, q * 32 + lane);
-        ++mcount;
-      }
     }
     if (use_tma && lane == 0) tma_store_wait_all();
+  } else if (warp >= 2 && warp < 4 && p.out_max != nullptr) {
+    // ------------------------------------------------------------------ fold: column maxima of the result
+    // As in lm2exp_kernel.cuh: warp 2 serves epilogue warps 4 and 5, warp 3 serves 6 and 7.  The other CTA of
+    // the pair and the other row tiles add their maxima with the same global reduction.
+    const int fw = warp - 2;
+    uint32_t nb[2] = {0, 0};
+    uint32_t mcount = 0;  // tiles whose column maxima this CTA has written
+    bool ok = true;
+    for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+      int r, n0, i0;
+      decode(tile, r, n0, i0);
+      const int my_i0 = i0 + static_cast<int>(rank) * BM;
+      if (my_i0 >= p.I) continue;  // this CTA's rows are padding: its epilogue stages nothing
+      const int slot = mcount & 1;
+      const int nchunks = min(BN / 32, (p.K - n0 + 31) / 32);
+      for (int c = 0; ok && c < nchunks; ++c) {
+#pragma unroll
+        for (int qq = 0; qq < 2; ++qq) {
+          const int q = 2 * fw + qq;
+          if (!(ok = mbar_wait_warp(&box_ready[q], nb[qq] & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+          ++nb[qq];
+          fold_staged_colmax(epi_stage + q * 4096, p.I - (my_i0 + q * 32), colbuf + slot * BN + c * 32, lane,
+                             &box_free[q]);
+        }
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cm_bar);
+      if (!(ok = mbar_wait_warp(cm_bar, mcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+      flush_tile_colmax(colbuf + slot * BN, BN, p.out_max + static_cast<int64_t>(r) * p.K + n0, p.K - n0, false,
+                        fw * 32 + lane);
+      ++mcount;
+    }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: this CTA's b boxes -> E, in place
     const int wv = warp - 8;

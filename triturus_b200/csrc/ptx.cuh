@@ -481,7 +481,10 @@ __device__ __forceinline__ float block_colmax_to_lanes(const float (&o)[32], boo
 // r * 128, 16-byte chunk g at position g ^ (r % 8)): eight 16-byte loads give a lane 8 rows of 4 columns, which
 // it folds in registers; two shuffle rounds fold the four row slots of the warp.  A third of the instructions
 // of block_colmax_to_lanes.  The caller has synchronised the warp after the writes.
-__device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_valid, int* cb, int lane) {
+// `box_free` (optional): an mbarrier on which one lane arrives as soon as every lane holds its part of the
+// box in registers, for a caller that reads the box on behalf of the warp that wants to overwrite it.
+__device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_valid, int* cb, int lane,
+                                                   uint64_t* box_free = nullptr) {
   const int g = lane & 7, rs = lane >> 3;
   float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
 #pragma unroll
@@ -494,6 +497,10 @@ __device__ __forceinline__ void fold_staged_colmax(const uint8_t* stg, int rows_
       mx.z = fmaxf(mx.z, v.z);
       mx.w = fmaxf(mx.w, v.w);
     }
+  }
+  if (box_free != nullptr) {
+    __syncwarp();  // the shuffles below would do, but the hand-back must not depend on their placement
+    if (lane == 0) mbar_arrive(box_free);
   }
 #pragma unroll
   for (int sh = 8; sh <= 16; sh <<= 1) {
@@ -525,12 +532,12 @@ __device__ __noinline__ void store_staged_rows(const uint8_t* stg, float* dst, i
   }
 }
 
-// End of a tile, called by the four epilogue warps after they have met at a barrier: thread te of 128 moves
-// columns te, te + 128, ... of the tile's buffer to gcol (a plain store when this tile alone covers the
+// End of a tile, called by the two fold warps after they have met at a barrier: thread te of 64 moves
+// columns te, te + 64, ... of the tile's buffer to gcol (a plain store when this tile alone covers the
 // column, else a reduction with the other row tiles) and resets the buffer.
 __device__ __forceinline__ void flush_tile_colmax(int* cb, int bn, float* gcol, int ncols_valid, bool exclusive,
                                                   int te) {
-  for (int c = te; c < bn; c += 128) {
+  for (int c = te; c < bn; c += 64) {
     const float v = __int_as_float(cb[c]);
     cb[c] = NEG_INF_BITS;
     if (c < ncols_valid) {
