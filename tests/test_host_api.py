@@ -168,6 +168,20 @@ def test_tma_ready_padding_rules():
     assert v3.stride(-1) == 1 and torch.equal(v3, t3)
 
 
+def test_transposed_a_is_kept_or_copied_by_cost():
+    """A transposed view of lm2exp's a is a legal MN-major operand; the wrapper keeps it when its estimate of
+    the transposing copy exceeds 16 % of its estimate of the kernel time, and copies otherwise or when the
+    view breaks the TMA rules (stride not a multiple of 4 elements)."""
+    view = torch.rand(2, 172, 300).transpose(1, 2)          # [2, 300, 172], i contiguous
+    assert _native._lm2exp_a_operand(view, 530) is view       # a third of all bytes: in place
+    assert _native._lm2exp_a_operand(view, 1 << 20) is not view  # a vanishing part of a huge problem: copy
+    odd = torch.rand(2, 40, 131).transpose(1, 2)            # j stride 131: not a multiple of 4
+    got = _native._lm2exp_a_operand(odd, 64)
+    assert got is not odd and got.stride(2) == 1 and torch.equal(got, odd)
+    plain = torch.rand(2, 300, 172)
+    assert _native._lm2exp_a_operand(plain, 530) is plain
+
+
 def test_workload_generators_are_seeded_and_shaped():
     from triturus_b200.workloads import WORKLOADS, make_inputs
 
