@@ -24,6 +24,19 @@ def test_shard_bounds_cover_the_batch():
         shard_bounds(4, 2, 2)
 
 
+def test_column_bounds_cover_the_columns_on_aligned_cuts():
+    from triturus_b200.sharding import column_bounds
+
+    for columns in (0, 3, 8, 100, 256, 8192, 530):
+        for world in (1, 2, 3, 8):
+            spans = [column_bounds(columns, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == columns
+            for (lo0, hi0), (lo1, hi1) in zip(spans, spans[1:]):
+                assert hi0 == lo1
+            if columns % 4 == 0:
+                assert all(lo % 4 == 0 for lo, _ in spans)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -45,19 +58,37 @@ def _worker(rank: int, world: int, port: int, batch: int, failures):
         x = torch.randn(batch, 3, 11, generator=g)
         full_lm = lm2exp_fp32(a, b)
         full_lt = lt2exp_fp32(w, x, b)
-        got = run_sharded(lm2exp_fp32, (a, b), gather=True)
+        got = run_sharded(lm2exp_fp32, (a, b), gather=True, axis="batch")
         if not torch.equal(got, full_lm):
             failures.append(f"rank {rank}: gathered lm2exp differs")
-        got = run_sharded(lt2exp_fp32, (w, x, b), gather=True)
+        got = run_sharded(lt2exp_fp32, (w, x, b), gather=True, axis="batch")
         if not torch.equal(got, full_lt):
             failures.append(f"rank {rank}: gathered lt2exp differs")
-        mine = run_sharded(lm2exp_fp32, (a, b), gather=False)
+        mine = run_sharded(lm2exp_fp32, (a, b), gather=False, axis="batch")
         lo, hi = shard_bounds(batch, rank, world)
         if not torch.equal(mine, full_lm[lo:hi]):
             failures.append(f"rank {rank}: local shard differs")
         sa, sb = shard_batch((a, b), rank, world)
         if sa.data_ptr() != a[lo:hi].data_ptr() or sb.shape[0] != hi - lo:
             failures.append(f"rank {rank}: shard_batch is not a view of the block")
+        # column sharding (what axis="auto" picks when the batch has fewer entries than there are ranks)
+        from triturus_b200.sharding import column_bounds, shard_columns
+
+        for op, xs, full in ((lm2exp_fp32, (a, b), full_lm), (lt2exp_fp32, (w, x, b), full_lt)):
+            got = run_sharded(op, xs, gather=True, axis="columns")
+            if got.shape != full.shape or not torch.allclose(got, full, rtol=1e-6, atol=1e-6):
+                failures.append(f"rank {rank}: column-gathered {op.__name__} differs")
+            mine = run_sharded(op, xs, gather=False, axis="columns")
+            klo, khi = column_bounds(b.shape[-1], rank, world)
+            if not torch.allclose(mine, full[..., klo:khi], rtol=1e-6, atol=1e-6):
+                failures.append(f"rank {rank}: local column shard of {op.__name__} differs")
+        auto = run_sharded(lm2exp_fp32, (a, b), gather=False)
+        want_cols = batch < world
+        if (auto.shape[0] == batch and auto.shape[-1] < b.shape[-1]) != want_cols:
+            failures.append(f"rank {rank}: axis=auto picked the wrong axis for batch {batch}")
+        sc = shard_columns((w, x, b), rank, world)
+        if sc[0].data_ptr() != w.data_ptr() or sc[2].shape[-1] != khi - klo:
+            failures.append(f"rank {rank}: shard_columns must replicate w and slice k")
     finally:
         dist.destroy_process_group()
 
