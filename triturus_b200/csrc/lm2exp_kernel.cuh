@@ -11,6 +11,8 @@
 //
 //   warp 0      TMA producer: per k-block MT a-tiles (128 x 32 fp32, K-major, 128B swizzle) and BN/32 b-boxes.
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.kind::tf32 (M = 128, N = BN, K = 8) and commits.
+//   warps 2-3   only when the column maxima of the result are wanted (chain links): read the epilogue warps'
+//               staged blocks back and fold them into max_i out[i, k], one value per tile column.
 //   warps 4-7   epilogue: tcgen05.ld, out = m + log(acc), staged per warp as a swizzled 32 x 32 box in shared
 //               memory and written by TMA stores (full 128-byte rows, clipped at the edges).
 //   warps 8-15  transform.  Warp w owns the 32-column group w % (BN/32); lane = 8 * row_slot + 16-byte chunk.
