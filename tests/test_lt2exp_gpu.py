@@ -242,6 +242,48 @@ def test_full_size_configs(name, batch, precision):
     tb.check_status()
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_cfg5_on_the_benchmarked_tile(precision):
+    """cfg5's own distribution (N(-40, 15), 0.5 % -inf, I * J = 16384) on the tile the full R = 64 benchmark runs:
+    256 x 256 (variant 2562), which the automatic choice only takes from R = 16 batch entries upwards.  The
+    float64 oracle checks one batch entry; the whole result is checked for NaN, for its -inf positions and
+    with the shift identity."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+    from triturus_b200.workloads import WORKLOADS, make_inputs
+
+    R = 16
+    wl = WORKLOADS["cfg5"].with_batch(R)
+    d = wl.dims
+    prec = 0 if precision == "tf32" else 1
+    # what bench.py runs at R = 64 is what this test pins
+    assert _native.LIB.triturus_b200_lt2exp_launches(64, d["S"], d["I"], d["J"], d["K"], prec, 0) == 1
+    w, a, b = make_inputs(wl, seed=0)
+    wd, ad, bd = w.cuda(), a.cuda(), b.cuda()
+    out = tb.lt2exp(wd, ad, bd, precision=precision, variant=2562)
+    auto = tb.lt2exp(wd, ad, bd, precision=precision)
+    tb.check_status()
+    assert not torch.isnan(out).any()
+    # a result is -inf exactly where a whole column of a or of b is -inf (w > 0 everywhere)
+    dead = (torch.isinf(ad).all(dim=1) | torch.isinf(bd).all(dim=1)).unsqueeze(1).expand_as(out)
+    assert torch.equal(out == float("-inf"), dead)
+    assert torch.equal(torch.isinf(auto), torch.isinf(out))
+    r = R - 3
+    want = orc.lt2exp_fp64(w[r : r + 1], a[r : r + 1], b[r : r + 1])
+    res = orc.compare_logspace(out[r : r + 1].cpu(), want, ATOL[precision])
+    assert res["ok"], res
+    # every other batch entry against the automatic tile choice (checked above on its own merits)
+    fin = torch.isfinite(out)
+    assert (out - auto)[fin].abs().max().item() <= 2 * ATOL[precision]
+    K = d["K"]
+    sa = torch.linspace(-2.0, 3.0, K).view(1, 1, -1).cuda()
+    sb = torch.linspace(4.0, -1.0, K).view(1, 1, -1).cuda()
+    out_s = tb.lt2exp(wd, ad + sa, bd + sb, precision=precision, variant=2562)
+    assert torch.equal(torch.isfinite(out_s), fin)
+    assert (out_s - sa - sb - out)[fin].abs().max().item() <= 2 * ATOL[precision]
+    tb.check_status()
+
+
 @pytest.mark.parametrize("variant", [1283, 1284, 1285])
 @pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1), (2, 129, 5, 1, 3), (2, 7, 9, 64, 257), (1, 300, 20, 31, 70),
                                    (3, 256, 16, 40, 384)])

@@ -3,8 +3,10 @@
 Such callers (arena-owned HBM, allocation-free serving loops, plugin hosts that receive only input and
 output buffers) use `triturus_b200_lm2exp_f32_static`, whose stabiliser scratch is a fixed array inside
 the library.  This test drives it through the C ABI with ctypes, twice in a row with different problem
-sizes so the second call finds the first call's leftovers in the shared array, and checks each result
-against the regular workspace entry point.  It also checks that oversize problems are refused.
+sizes.  Both calls are pinned to the kernels that take their stabiliser from the scratch array (the
+pre-pass writes it, the contraction kernel reads it), so the second call really finds the first call's
+leftovers there.  Each result is checked against the float64 CPU oracle and, bit for bit, against the
+entry point that takes a caller workspace.  It also checks that oversize problems are refused.
 
 The file name sorts last on purpose: a failure here cannot hide the rest of the suite under `-x`.
 """
@@ -15,8 +17,12 @@ import pytest
 import torch
 
 from conftest import ATOL
+from oracle import logspace_oracle as orc
 
 pytestmark = pytest.mark.gpu
+
+
+PREPASS = 100000  # variant code: stabiliser from the pre-pass through the scratch array, never the fused max pass
 
 
 def _call_static(a, b, precision):
@@ -30,7 +36,7 @@ def _call_static(a, b, precision):
     rc = _native.LIB.triturus_b200_lm2exp_f32_static(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K,
         _native._i64(a.stride()), _native._i64(b.stride()), _native._i64(out.stride()),
-        precision, 0, status.data_ptr(), stream,
+        precision, PREPASS, status.data_ptr(), stream,
     )  # fmt: skip
     assert rc == 0, _native.strerror(rc)
     torch.cuda.synchronize()
@@ -39,7 +45,7 @@ def _call_static(a, b, precision):
 
 
 @pytest.mark.parametrize("precision", [0, 1])
-def test_static_scratch_entry_matches_workspace_entry_twice(precision):
+def test_static_scratch_entry_matches_oracle_twice(precision):
     from triturus_b200 import _native
 
     name = "tf32" if precision == 0 else "3xtf32"
@@ -47,16 +53,19 @@ def test_static_scratch_entry_matches_workspace_entry_twice(precision):
     # first call fills a large part of the built-in array, second call is smaller and has other maxima
     shapes = [(8, 300, 160, 4096), (3, 130, 96, 520)]
     for R, I, J, K in shapes:
-        a = torch.rand(R, I, J, generator=g).cuda()
-        b = (torch.randn(R, J, K, generator=g) * 6.0 + 80.0 * torch.randn(R, 1, K, generator=g)).cuda()
+        # both calls launch the pre-pass and the contraction kernel (two launches): the array is written and read
+        assert _native.LIB.triturus_b200_lm2exp_launches(R, I, J, K, precision, PREPASS) == 2
+        a = torch.rand(R, I, J, generator=g)
+        b = torch.randn(R, J, K, generator=g) * 6.0 + 80.0 * torch.randn(R, 1, K, generator=g)
         b[0, :, 3] = float("-inf")
-        got = _call_static(a, b, precision)
-        want = _native._lm2exp_impl(a, b, precision, 0)
+        got = _call_static(a.cuda(), b.cuda(), precision)
+        res = orc.compare_logspace(got.cpu(), orc.lm2exp_fp64(a, b), ATOL[name])
+        assert res["ok"], res
+        assert torch.all(got[0, :, 3] == float("-inf"))
+        # same kernels, same stabiliser values, other scratch memory: identical bits
+        same = _native._lm2exp_impl(a.cuda(), b.cuda(), precision, PREPASS)
         torch.cuda.synchronize()
-        assert not torch.isnan(got).any()
-        assert torch.equal(got == float("-inf"), want == float("-inf"))
-        fin = torch.isfinite(want)
-        assert (got[fin] - want[fin]).abs().max().item() <= ATOL[name]
+        assert torch.equal(got, same)
 
 
 def test_static_scratch_entry_rejects_oversize_problems():

@@ -179,6 +179,10 @@ using LmT_256_2 = Lm2expCfg<256, 2, 0, 3>;
 using LmX_128_1 = Lm2expCfg<128, 1, 1, 3>;
 using LmX_128_2 = Lm2expCfg<128, 2, 1, 2>;
 
+// plain TF32 with chunked re-summation of the accumulator, for contractions of more than 32 K terms
+using LmP_128_1 = Lm2expCfg<128, 1, 0, 6, true>;
+using LmP_128_2 = Lm2expCfg<128, 2, 0, 4, true>;
+
 using LmPairT = Lm2expPairCfg<0, 6>;
 using LmPairX = Lm2expPairCfg<1, 3>;
 
@@ -231,7 +235,8 @@ static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt)
 // All kernels are bound by the shared-memory pipe, and a larger tile moves fewer bytes through it per MAC
 // (the factors are bytes per k-block / 128 B per clock over the k-block's tensor cycles), so a larger tile
 // wins unless it leaves the last wave mostly empty.
-static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256, bool in_place_transform) {
+static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256, bool in_place_transform,
+                        int max_acc_cols = 512) {
   const int sms = sm_count();
   const int mt_max = rows > 128 ? 2 : 1;
   const int bn_max = (cols > 128 && allow_bn256) ? 256 : 128;
@@ -239,6 +244,7 @@ static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256,
   double best_cost = 1e300;
   for (int bn = 128; bn <= bn_max; bn *= 2) {
     for (int mt = 1; mt <= mt_max; ++mt) {
+      if (mt * bn > max_acc_cols) continue;  // the caller needs TMEM columns beside the accumulator
       const int64_t waves = (tile_count(R, rows, cols, bn, mt) + sms - 1) / sms;
       // per k-block: a-tiles in + operand read, b in (+ read + write back when transformed in place),
       // operand read of b once per row block
@@ -261,7 +267,12 @@ struct Lm2expPlan {
   bool pair;    // 256 x 256 tile on a pair of CTAs
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
   bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
+  bool promote_tf32;      // plain TF32 over more than kLongContraction terms: accumulator re-summed in chunks
 };
+
+// Contractions longer than this run with the chunked re-summation of the accumulator in plain TF32 too: the
+// tensor core's truncating adds lose ~1.5e-8 per term (2.6e-4 in log space at 16 K terms, 2.5e-3 at 256 K).
+constexpr int64_t kLongContraction = 32768;
 
 // have_m: the caller supplies the stabiliser, so the tile is chosen as usual but no max pass of either kind runs.
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
@@ -277,9 +288,11 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // accumulator, ~1.2e-8 per term, would use up the 3xTF32 tolerance: only the single-CTA kernel re-sums
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
-    const bool want_pair =
-        stab_mode != 2 && !long_3x && I > 256 && K > 128 && tile_count(R, I, K, 256, 2) >= sm_count() / 4;
-    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32, true);
+    const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
+    const bool want_pair = stab_mode != 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
+                           tile_count(R, I, K, 256, 2) >= sm_count() / 4;
+    // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
+    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
   int bn = tile_variant / 10;
   const int mt = tile_variant % 10;
@@ -300,6 +313,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   out->pair = pair;
   out->fused = fused && !have_m;
   out->colmax_exclusive = !pair && I <= 128 * mt;
+  out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
   return TRITURUS_B200_OK;
 }
 
@@ -488,6 +502,8 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
     return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, to, p, st);
   }
   if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st);
+  if (plan.promote_tf32)
+    return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmP_128_1>(ta, tb, to, p, st);
   return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st);
 }
 
@@ -626,23 +642,32 @@ using LtT_256_2 = Lt2expCfg<256, 2, 0, 3, 8>;
 using LtX_128_1 = Lt2expCfg<128, 1, 1, 3, 8>;
 using LtX_128_2 = Lt2expCfg<128, 2, 1, 2, 8>;
 using LtX_256_1 = Lt2expCfg<256, 1, 1, 2, 8>;
+// plain TF32 with chunked re-summation of the accumulator (contractions of more than 32 K terms)
+using LtP_128_1 = Lt2expCfg<128, 1, 0, 6, 8, true>;
+using LtP_128_2 = Lt2expCfg<128, 2, 0, 4, 8, true>;
+using LtP_256_1 = Lt2expCfg<256, 1, 0, 4, 8, true>;
 
 }  // namespace tb200
 
 // Decodes SPLIT * 10000 + BN * 10 + MT, filling in the automatic tile shape.
-static int lt2exp_variant(int variant, int precision, int64_t R, int64_t S, int64_t K, int* bn, int* mt,
-                          int* split) {
+// *promote: plain TF32 over a contraction of more than kLongContraction terms on a tile whose accumulator
+// leaves room for a master copy in TMEM (the automatic choice is restricted to such tiles; an explicit
+// 256 x 256 tile or TMEM-operand variant is honoured and runs without the re-summation).
+static int lt2exp_variant(int variant, int precision, int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int* bn,
+                          int* mt, int* split, bool* promote) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
   *split = variant / 10000;
   int tile = variant % 10000;
+  const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && I * ((J + 31) / 32 * 32) > tb200::kLongContraction;
   if (tile == 0) {
-    tile = tb200::auto_variant(R, S, K, true, false);
+    tile = tb200::auto_variant(R, S, K, true, false, long_tf ? 256 : 512);
     // 128 rows x 256 columns in TF32: the kernel that keeps the generated operand in TMEM moves a third of
     // the shared-memory bytes per k-block (measured 8 % faster on such tiles).
-    if (tile == 2561 && precision == TRITURUS_B200_PRECISION_TF32) tile = 1285;
+    if (tile == 2561 && precision == TRITURUS_B200_PRECISION_TF32 && !long_tf) tile = 1285;
   }
   *bn = tile / 10;
   *mt = tile % 10;
+  *promote = long_tf && (tile == 1281 || tile == 1282 || tile == 2561);
   // operand in TMEM: 128 columns x 128 / 256 rows (1283 / 1284), 256 columns x 128 rows (1285)
   if (*bn == 128 && (*mt == 3 || *mt == 4 || *mt == 5)) return TRITURUS_B200_OK;
   if ((*bn != 128 && *bn != 256) || (*mt != 1 && *mt != 2)) return TRITURUS_B200_EINVAL;
@@ -659,8 +684,12 @@ static int lt2exp_check_dims(int64_t R, int64_t S, int64_t I, int64_t J, int64_t
 }
 
 template <class... Args>
-static int lt2exp_dispatch(int precision, int bn, int mt, Args... args) {
+static int lt2exp_dispatch(int precision, int bn, int mt, bool promote, Args... args) {
   using namespace tb200;
+  if (promote) {
+    if (bn == 256) return launch_lt2exp<LtP_256_1>(args...);
+    return mt == 2 ? launch_lt2exp<LtP_128_2>(args...) : launch_lt2exp<LtP_128_1>(args...);
+  }
   if (mt == 3 || mt == 4 || mt == 5) {
     if (precision != TRITURUS_B200_PRECISION_TF32) return TRITURUS_B200_EINVAL;
     if (mt == 5) return launch_lt2exp_tmem<LtM_1x2>(args...);
@@ -679,7 +708,8 @@ extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, in
   int rc = lt2exp_check_dims(R, S, I, J, K, precision);
   if (rc != TRITURUS_B200_OK) return rc;
   int bn, mt, split;
-  rc = lt2exp_variant(variant, precision, R, S, K, &bn, &mt, &split);
+  bool promote;
+  rc = lt2exp_variant(variant, precision, R, S, I, J, K, &bn, &mt, &split, &promote);
   if (rc != TRITURUS_B200_OK) return rc;
   tb200::Lt2expParams p{};
   p.R = static_cast<int>(R);
@@ -689,7 +719,7 @@ extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, in
   p.K = static_cast<int>(K);
   int n = 0;
   CUtensorMap none{};
-  rc = lt2exp_dispatch(precision, bn, mt, none, p, split, static_cast<cudaStream_t>(nullptr), &n);
+  rc = lt2exp_dispatch(precision, bn, mt, promote, none, p, split, static_cast<cudaStream_t>(nullptr), &n);
   return rc == TRITURUS_B200_OK ? n : rc;
 }
 
@@ -725,8 +755,9 @@ static int lt2exp_run(const float* w, const float* a, const float* b, float* out
     return TRITURUS_B200_EALIGN;
 
   int bn, mt, split;
+  bool promote;
   {
-    const int rc = lt2exp_variant(variant, precision, R, S, K, &bn, &mt, &split);
+    const int rc = lt2exp_variant(variant, precision, R, S, I, J, K, &bn, &mt, &split, &promote);
     if (rc != TRITURUS_B200_OK) return rc;
   }
 
@@ -768,7 +799,8 @@ static int lt2exp_run(const float* w, const float* a, const float* b, float* out
                                  static_cast<cudaStream_t>(stream)>>>(out_colmax, n);
   }
 
-  return lt2exp_dispatch(precision, bn, mt, tw, p, split, static_cast<cudaStream_t>(stream), static_cast<int*>(nullptr));
+  return lt2exp_dispatch(precision, bn, mt, promote, tw, p, split, static_cast<cudaStream_t>(stream),
+                         static_cast<int*>(nullptr));
 }
 
 extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,

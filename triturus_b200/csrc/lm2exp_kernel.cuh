@@ -47,7 +47,7 @@ struct Lm2expParams {
   int* status;
 };
 
-template <int BN_, int MT_, int PREC_, int NS_>
+template <int BN_, int MT_, int PREC_, int NS_, bool PROMOTE_ = (PREC_ != 0)>
 struct Lm2expCfg {
   static constexpr int BM = 128, BK = 32, NTW = 8;
   static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_;
@@ -61,13 +61,13 @@ struct Lm2expCfg {
   static constexpr int ROWS_PER_WARP = BK / RP;
   static constexpr int ACC_COLS = MT * BN;
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
-  // 3xTF32 only: contractions longer than CHUNK k-blocks are accumulated chunk by chunk and the chunks are
+  // 3xTF32, and the plain-TF32 PROMOTE instances: contractions longer than CHUNK k-blocks are accumulated chunk by chunk and the chunks are
   // added into a master copy in TMEM with rounded fp32 adds (the tensor core's own accumulation truncates:
   // measured drift 2.6e-4 in log space at J = 16 K, 2.4e-3 at J = 256 K).  The master copy takes the TMEM
   // columns from MASTER_COL on; with 256 accumulator columns that is the second buffer, so a promoting
   // launch runs single-buffered.
-  static constexpr bool PROMOTE = PREC != 0;
-  static constexpr int CHUNK = 32;
+  static constexpr bool PROMOTE = PROMOTE_;
+  static constexpr int CHUNK = PREC ? 32 : 128;  // plain TF32 (PROMOTE instances, J > 32 K): every 4 K terms
   static constexpr int MASTER_COL = (ACC_COLS <= 128) ? 2 * ACC_COLS : ACC_COLS;
   static constexpr int NBUF_PROMOTE = (ACC_COLS <= 128) ? 2 : 1;
   static constexpr int TMEM_USED = PROMOTE ? (MASTER_COL + ACC_COLS) : NBUF * ACC_COLS;

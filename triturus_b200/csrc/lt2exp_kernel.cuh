@@ -25,13 +25,14 @@
 // epilogue adds its raw accumulator into the zero-filled output with red.global.add and
 // lt2exp_finish_kernel then turns the sums into (ma + mb) + log(sum) in place.
 //
-// Accumulator promotion (3xTF32 only).  The tensor core adds into its fp32 accumulator with truncation, so a
+// Accumulator promotion (3xTF32 always; plain TF32 in the PROMOTE instances the launcher picks for contractions
+// of more than 32 K terms).  The tensor core adds into its fp32 accumulator with truncation, so a
 // sum of positive terms drifts low by about half an ulp per MMA: ~3e-8 relative per 8 contraction terms,
 // 1e-4 after 32 K terms and 2.5e-3 after 256 K, far more than the 3xTF32 operand error.  In 3xTF32 mode
 // the MMA warp therefore starts a fresh TMEM accumulator every CHUNK k-blocks and the epilogue warps, idle
 // during the main loop, add each finished chunk into a master copy kept in a further TMEM region with
-// round-to-nearest fp32 adds (tcgen05.ld, add, tcgen05.st).  Plain TF32 keeps one chunk per work item: its
-// operand rounding dominates up to ~100 K terms and the reference's TF32 path has the same drift.
+// round-to-nearest fp32 adds (tcgen05.ld, add, tcgen05.st).  Plain TF32 on shorter contractions keeps one chunk
+// per work item: the drift stays below 3e-4 there, well inside the 2e-3 tolerance of that mode.
 #pragma once
 
 #include "ptx.cuh"
@@ -59,7 +60,7 @@ struct Lt2expParams {
   float* out_max;
 };
 
-template <int BN_, int MT_, int PREC_, int NS_, int NTW_>
+template <int BN_, int MT_, int PREC_, int NS_, int NTW_, bool PROMOTE_ = (PREC_ != 0)>
 struct Lt2expCfg {
   static constexpr int BM = 128, BK = 32;
   static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_, NTW = NTW_;
@@ -68,8 +69,10 @@ struct Lt2expCfg {
   static constexpr int B_TILE = BN * BK * 4;
   static constexpr int STAGE = NCOPY * (MT * A_TILE + B_TILE);
   static constexpr int ACC_COLS = MT * BN;
-  static constexpr bool PROMOTE = PREC != 0;
-  static constexpr int CHUNK = 32;  // k-blocks accumulated by the tensor core before a promotion
+  static constexpr bool PROMOTE = PROMOTE_;
+  // k-blocks (of 32 terms) accumulated by the tensor core before a promotion: 1 K terms keep the drift near
+  // 1e-5 for 3xTF32; plain TF32 (2e-3 budget, operand rounding ~1e-3) promotes every 4 K terms (~6e-5).
+  static constexpr int CHUNK = PREC ? 32 : 128;
   // Accumulator buffers the MMA warp rotates through, and the master copy behind them when promoting.
   static constexpr int NBUF = PROMOTE ? ((3 * ACC_COLS <= 512) ? 2 : 1) : ((2 * ACC_COLS <= 512) ? 2 : 1);
   static constexpr int MASTER_COL = NBUF * ACC_COLS;
