@@ -106,9 +106,14 @@ int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, i
  *            automatic choice uses where it would otherwise take 2561)
  *            and SPLIT the number of slices the contraction over (i, j) of every output tile is cut into, the
  *            counterpart of the reference's NUM_SPLITS and mode argument (triturus/lt2exp.py:533-541):
- *            0 = automatic (split when the output tiles would occupy fewer than half the SMs), 1 = never
- *            (mode "unsplit"), n >= 2 = n slices (fewer if a slice would drop below 16 k-blocks), 9999 = as
- *            automatic but at least two slices (mode "split").  A split call launches three kernels: zero-fill
+ *            0 = automatic (slices when the output tiles would occupy fewer than half the SMs; when the last
+ *            wave of tiles would be less than 90 % full and a tile's contraction is at least 8192 terms long,
+ *            the k-blocks of all tiles are laid end to end and every CTA takes the same length of that line,
+ *            across tile borders), 1 = never (mode "unsplit"), n >= 2 = n slices (fewer if a slice would drop
+ *            below 16 k-blocks), 9998 = the end-to-end form in any case, 9999 = as automatic but at least two
+ *            slices (mode "split").  Plain TF32 over more than 32768 terms re-sums its accumulator every 4096
+ *            terms with rounded adds (automatic tiles only leave room for that; an explicit 2562 / 128x tile is
+ *            honoured and runs without).  A split call launches three kernels: zero-fill
  *            of out, the slices adding their partial sums into out with fp32 reductions (so the last bits
  *            depend on arrival order, as they do under the reference's spin lock, triturus/lt2exp.py:498-506),
  *            and the in-place log pass.  Unsplit results are deterministic.
@@ -117,6 +122,14 @@ int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, i
 /* Number of kernels one triturus_b200_lt2exp_f32 call launches for these arguments on the current device
  * (1, or 3 when the contraction is split); negative on invalid arguments. */
 int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
+/* What a triturus_b200_lt2exp_f32 call with these arguments runs on the current device, as the explicit variant
+ * code that pins it: SPLIT * 10000 + BN * 10 + MT with SPLIT = 1 (whole tiles), the slice count, or 9998 (end to
+ * end).  The counterpart of reading the reference's autotuner choice (triturus/lt2exp.py:9-75,78-222); negative
+ * on invalid arguments. */
+int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
+/* The same for triturus_b200_lm2exp_f32: STAB * 100000 + BN * 10 + MT with STAB = 1 (pre-pass) or 2 (fused max
+ * pass); negative on invalid arguments. */
+int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
                              int64_t I, int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
                              const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
@@ -145,6 +158,16 @@ int triturus_b200_lt2exp_chain_f32(const float* w, const float* a, const float* 
  */
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
                              void* stream);
+
+/*
+ * Self-test of the error path behind `status_dev` (no counterpart in the reference, whose kernels have no waits
+ * that could time out apart from the unbounded spin lock of triturus/lt2exp.py:498-506).  Launches one 64-thread
+ * block in which a warp waits on a barrier that nobody signals, with a wait limit of `limit_cycles` GPU clock
+ * cycles (1e3 ... 2e8, i.e. at most ~0.1 s) instead of the ~1.5 s the kernels use.  The wait gives up, the other
+ * warp of the block leaves its own wait on seeing the abort flag, and the kernel returns by itself with the code
+ * 105 ("device: setup wait timed out") in *status_dev.  Nothing traps, faults or spins without a bound.
+ */
+int triturus_b200_selftest_wait_timeout(int32_t* status_dev, int64_t limit_cycles, void* stream);
 
 /*
  * lm2exp for callers that cannot allocate device memory.  (No counterpart in the reference: its wrapper

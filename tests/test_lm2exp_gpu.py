@@ -40,6 +40,42 @@ def test_golden(name, precision):
     _assert_close(got, g["a"], g["b"], precision)
 
 
+@pytest.mark.parametrize("shape", [(1, 256, 32, 256), (2, 300, 100, 260), (3, 257, 33, 516), (2, 1000, 250, 1000),
+                                   (1, 130, 1024, 40), (5, 300, 171, 530)])
+def test_tmem_operand_pair_kernel(shape):
+    """Variant 2566: the CTA-pair kernel that keeps exp(b - m) in tensor memory (plain TF32), on ragged shapes with
+    isolated -inf entries, an all -inf column, rows past I, columns past K and a partial last k-block.  Its
+    arithmetic is that of the shared-memory pair kernel (2564) in the same order, so the two agree bit for bit."""
+    import triturus_b200 as tb
+
+    R, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    a = torch.rand(R, I, J, generator=g)
+    b = torch.randn(R, J, K, generator=g) * 6.0 + 50.0 * torch.randn(R, 1, K, generator=g)
+    b[0, :, min(3, K - 1)] = float("-inf")
+    b[torch.rand(R, J, K, generator=g) < 0.01] = float("-inf")
+    from triturus_b200 import _native
+
+    assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, 0, 2566) == 102566
+    got = tb.lm2exp(a.cuda(), b.cuda(), precision="tf32", variant=2566)
+    same = tb.lm2exp(a.cuda(), b.cuda(), precision="tf32", variant=2564)
+    tb.check_status()
+    assert torch.all(got[0, :, min(3, K - 1)] == float("-inf"))
+    _assert_close(got.cpu(), a, b, "tf32")
+    assert torch.equal(got, same)
+    with pytest.raises(tb.NativeLibraryError):
+        tb.lm2exp(a.cuda(), b.cuda(), precision="3xtf32", variant=2566)
+
+
+def test_tmem_operand_pair_kernel_unaligned_result():
+    """K not a multiple of 4: the wrapper pads b, the result rows are not 16-byte aligned and are written row by row."""
+    g = torch.Generator().manual_seed(99)
+    a = torch.rand(2, 270, 70, generator=g)
+    b = torch.randn(2, 70, 263, generator=g) * 4.0
+    got = _run(a, b, precision="tf32", variant=2566)
+    _assert_close(got, a, b, "tf32")
+
+
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_variants_on_ragged_shape(precision, variant):
@@ -193,6 +229,29 @@ def test_long_contraction_3xtf32(J, variant):
     assert torch.all(got[1, :, 3] == float("-inf"))
     res = orc.compare_logspace(got, want, ATOL["3xtf32"])
     assert res["ok"], res
+
+
+@pytest.mark.parametrize("variant", [0, 101281, 201282])
+def test_long_contraction_plain_tf32(variant):
+    """Plain TF32 over more than 32 K terms runs on the kernels that re-sum their accumulator every 4096 terms, so
+    the stated 2e-3 holds whatever the length of the contraction (the tensor core's truncating adds alone lose
+    7.8e-4 at 64 K terms and 2.5e-3 at 256 K, on top of the operand rounding)."""
+    from triturus_b200 import _native
+
+    J = 140000
+    g = torch.Generator().manual_seed(variant)
+    I = 200 if variant in (0, 201282) else 100
+    a = torch.rand(1, I, J, generator=g)
+    b = torch.randn(1, J, 140, generator=g)
+    b[0, :, 3] = float("-inf")
+    assert _native.LIB.triturus_b200_lm2exp_plan(1, I, J, 140, 0, variant) % 100000 // 10 == 128
+    got = _run(a, b, precision="tf32", variant=variant)
+    want = orc.lm2exp_fp64(a, b)
+    assert torch.all(got[0, :, 3] == float("-inf"))
+    res = orc.compare_logspace(got, want, ATOL["tf32"])
+    assert res["ok"], res
+    # the drift alone would be ~1.7e-3 here; with the re-summation the error is the operand rounding
+    assert res["max_abs_err"] < 1.2e-3, res
 
 
 @pytest.mark.parametrize("variant", [0, 1281, 1282, 2561, 2562, 2564])

@@ -62,7 +62,7 @@ def test_deterministic_algorithms_switch_off_the_split():
     assert torch.equal(got, base)
 
 
-SPLITS = [2, 3, 7, 16, 64, 9999]
+SPLITS = [2, 3, 7, 16, 64, 9998, 9999]  # 9998: k-blocks of all tiles end to end, equal share per CTA
 
 
 @pytest.mark.parametrize("split", SPLITS)
@@ -242,12 +242,56 @@ def test_full_size_configs(name, batch, precision):
     tb.check_status()
 
 
+@pytest.mark.parametrize("tile", [0, 1281, 1282, 2561, 2562, 1283, 1285])
 @pytest.mark.parametrize("precision", PRECISIONS)
-def test_cfg5_on_the_benchmarked_tile(precision):
-    """cfg5's own distribution (N(-40, 15), 0.5 % -inf, I * J = 16384) on the tile the full R = 64 benchmark runs:
-    256 x 256 (variant 2562), which the automatic choice only takes from R = 16 batch entries upwards.  The
-    float64 oracle checks one batch entry; the whole result is checked for NaN, for its -inf positions and
-    with the shift identity."""
+def test_contraction_end_to_end_ranges_cross_tiles(precision, tile):
+    """The end-to-end form on a shape where every CTA's range is longer than a tile's contraction (40 k-blocks),
+    so ranges start and end inside j-chunk rows and cover parts of two or three tiles."""
+    if precision == "3xtf32" and tile in (2562, 1283, 1285):
+        pytest.skip("no 256 x 256 tile and no TMEM-operand kernel in 3xTF32")
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(808)
+    R, S, I, J, K = 16, 256, 20, 64, 1024
+    w = torch.rand(R, S, I, J, generator=g)
+    a = torch.randn(R, I, K, generator=g) * 5.0
+    b = torch.randn(R, J, K, generator=g) * 5.0 - 30.0
+    b[torch.rand(R, J, K, generator=g) < 0.02] = float("-inf")
+    a[3, :, 77] = float("-inf")
+    variant = 9998 * 10000 + tile
+    prec = 0 if precision == "tf32" else 1
+    assert _native.LIB.triturus_b200_lt2exp_launches(R, S, I, J, K, prec, variant) == 3
+    assert _native.LIB.triturus_b200_lt2exp_plan(R, S, I, J, K, prec, variant) // 10000 == 9998
+    got = _run(w, a, b, precision=precision, variant=variant)
+    want = orc.lt2exp_fp64(w, a, b)
+    assert torch.all(got[3, :, 77] == float("-inf"))
+    assert torch.equal(got == float("-inf"), want == float("-inf"))
+    _assert_close(got, w, a, b, precision, want)
+
+
+def test_automatic_choice_balances_a_ragged_last_wave():
+    """R = 8 entries of cfg5's shape are 128 tiles of 256 x 256 on 148 SMs: the automatic choice lays the
+    contractions end to end; the full R = 64 (6.9 waves) and a deterministic call keep whole tiles."""
+    from triturus_b200 import _native
+
+    plan = _native.LIB.triturus_b200_lt2exp_plan
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if sms != 148:
+        pytest.skip("the tile counts in this test are for 148 SMs")
+    assert plan(8, 256, 128, 128, 4096, 0, 0) == 9998 * 10000 + 2562
+    assert plan(64, 256, 128, 128, 4096, 0, 0) == 1 * 10000 + 2562
+    assert plan(8, 256, 128, 128, 4096, 0, 1 * 10000) == 1 * 10000 + 2562
+    # cfg4: a tile's contraction (128 k-blocks) is too short to pay for the two extra launches
+    assert plan(16, 128, 64, 64, 2048, 0, 0) == 1 * 10000 + 1285
+
+
+@pytest.mark.parametrize("variant", [1 * 10000 + 2562, 9998 * 10000 + 2562])
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_cfg5_on_the_benchmarked_tile(precision, variant):
+    """cfg5's own distribution (N(-40, 15), 0.5 % -inf, I * J = 16384) on the tile the benchmarks run: 256 x 256
+    as whole tiles (12562, what the full R = 64 runs on one GPU) and with the contractions end to end (99982562,
+    what R = 64 / N runs per GPU on 2, 4 and 8 GPUs).  The float64 oracle checks one batch entry; the whole
+    result is checked for NaN, for its -inf positions and with the shift identity."""
     import triturus_b200 as tb
     from triturus_b200 import _native
     from triturus_b200.workloads import WORKLOADS, make_inputs
@@ -256,11 +300,14 @@ def test_cfg5_on_the_benchmarked_tile(precision):
     wl = WORKLOADS["cfg5"].with_batch(R)
     d = wl.dims
     prec = 0 if precision == "tf32" else 1
-    # what bench.py runs at R = 64 is what this test pins
-    assert _native.LIB.triturus_b200_lt2exp_launches(64, d["S"], d["I"], d["J"], d["K"], prec, 0) == 1
+    if precision == "tf32" and torch.cuda.get_device_properties(0).multi_processor_count == 148:
+        # what bench.py runs at R = 64 (one GPU) and at R = 8 (eight GPUs) is what this test pins
+        plan = _native.LIB.triturus_b200_lt2exp_plan
+        assert plan(64, d["S"], d["I"], d["J"], d["K"], prec, 0) == 12562
+        assert plan(8, d["S"], d["I"], d["J"], d["K"], prec, 0) == 99982562
     w, a, b = make_inputs(wl, seed=0)
     wd, ad, bd = w.cuda(), a.cuda(), b.cuda()
-    out = tb.lt2exp(wd, ad, bd, precision=precision, variant=2562)
+    out = tb.lt2exp(wd, ad, bd, precision=precision, variant=variant)
     auto = tb.lt2exp(wd, ad, bd, precision=precision)
     tb.check_status()
     assert not torch.isnan(out).any()
@@ -278,7 +325,7 @@ def test_cfg5_on_the_benchmarked_tile(precision):
     K = d["K"]
     sa = torch.linspace(-2.0, 3.0, K).view(1, 1, -1).cuda()
     sb = torch.linspace(4.0, -1.0, K).view(1, 1, -1).cuda()
-    out_s = tb.lt2exp(wd, ad + sa, bd + sb, precision=precision, variant=2562)
+    out_s = tb.lt2exp(wd, ad + sa, bd + sb, precision=precision, variant=variant)
     assert torch.equal(torch.isfinite(out_s), fin)
     assert (out_s - sa - sb - out)[fin].abs().max().item() <= 2 * ATOL[precision]
     tb.check_status()

@@ -22,12 +22,15 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lm2exp_workspace_bytes",
     "triturus_b200_lm2exp_launches",
     "triturus_b200_lt2exp_launches",
+    "triturus_b200_lt2exp_plan",
+    "triturus_b200_lm2exp_plan",
     "triturus_b200_lm2exp_f32",
     "triturus_b200_lm2exp_chain_launches",
     "triturus_b200_lm2exp_chain_f32",
     "triturus_b200_lt2exp_f32",
     "triturus_b200_lt2exp_chain_f32",
     "triturus_b200_colmax_f32",
+    "triturus_b200_selftest_wait_timeout",
     "triturus_b200_lm2exp_static_max_columns",
     "triturus_b200_lm2exp_f32_static",
 )
@@ -39,14 +42,17 @@ class NativeLibraryError(RuntimeError):
 
 def _open() -> ctypes.CDLL:
     path = _build.LIB_PATH
-    if not path.exists():
-        # First use in a fresh checkout: build in-tree.  A failure here is fatal by design.
+    if _build.is_stale():
+        # First use in a fresh checkout, or a source file is newer than the library: build in-tree (a no-op
+        # when the library is fresh).  Without a compiler an existing library is used as it is; a missing one
+        # is fatal by design.
         try:
             _build.build()
         except Exception as exc:  # noqa: BLE001
-            raise NativeLibraryError(
-                f"{path} is missing and could not be built ({exc}); run `python -m triturus_b200.build`"
-            ) from exc
+            if not path.exists():
+                raise NativeLibraryError(
+                    f"{path} is missing and could not be built ({exc}); run `python -m triturus_b200.build`"
+                ) from exc
     try:
         return ctypes.CDLL(os.fspath(path))
     except OSError as exc:
@@ -80,6 +86,10 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.triturus_b200_lm2exp_launches.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int, c_int]
     lib.triturus_b200_lt2exp_launches.restype = c_int
     lib.triturus_b200_lt2exp_launches.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]
+    lib.triturus_b200_lt2exp_plan.restype = c_int
+    lib.triturus_b200_lt2exp_plan.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]
+    lib.triturus_b200_lm2exp_plan.restype = c_int
+    lib.triturus_b200_lm2exp_plan.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int, c_int]
     lib.triturus_b200_lm2exp_f32.restype = c_int
     lib.triturus_b200_lm2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
@@ -109,6 +119,8 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, i64p, i64p, i64p,
         c_int, c_int, c_void_p, c_void_p,
     ]  # fmt: skip
+    lib.triturus_b200_selftest_wait_timeout.restype = c_int
+    lib.triturus_b200_selftest_wait_timeout.argtypes = [c_void_p, c_int64, c_void_p]
     lib.triturus_b200_colmax_f32.restype = c_int
     lib.triturus_b200_colmax_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, i64p, c_void_p]
     return lib

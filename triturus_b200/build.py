@@ -7,6 +7,7 @@ GPU is needed to build.
 
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -34,12 +35,24 @@ def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h"))
 
 
+STAMP_PATH = LIB_PATH.with_suffix(".so.sources")  # digest of the sources the library was built from
+
+
+def _digest() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for src in _sources():
+        h.update(src.name.encode())
+        h.update(src.read_bytes())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
-    """True when the library is missing or older than any of its sources."""
-    if not LIB_PATH.exists():
+    """True when the library is missing or was built from other sources than the ones on disk.  The check is
+    by content, not by time stamp: a copy of the tree to another machine must not look stale."""
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
-    return any(src.stat().st_mtime > built for src in _sources())
+    return STAMP_PATH.read_text().strip() != _digest()
 
 
 def find_nvcc() -> str | None:
@@ -60,12 +73,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     cmd = [nvcc, *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    # one temporary file per process: ranks of one job that all find the library stale do not write into each
+    # other's output, and os.replace makes whichever finishes last the library (they are identical)
+    tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
     cmd += ["-o", str(tmp), *[str(p) for p in sorted(CSRC.glob("*.cu"))]]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp, LIB_PATH)
+    STAMP_PATH.write_text(_digest() + "\n")
     if verbose:
         sys.stderr.write(proc.stderr)
     return LIB_PATH

@@ -12,6 +12,7 @@
 #include "../../include/triturus_b200.h"
 #include "lm2exp_kernel.cuh"
 #include "lm2exp_pair_kernel.cuh"
+#include "lm2exp_tspair_kernel.cuh"
 #include "lt2exp_kernel.cuh"
 #include "lt2exp_tmem_kernel.cuh"
 
@@ -26,6 +27,9 @@ template <bool VEC>
 __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
                                                       int64_t s0, int64_t s1) {
   __shared__ float part[8][32];
+  // The contraction kernel that consumes m may be launched as a programmatic dependent: let it start its set-up
+  // (barriers, tensor memory, first operand tiles) as soon as every block of this grid is running.
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.y;
   const int c0 = blockIdx.x * 32;
@@ -77,6 +81,32 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
 // Fills m[0..n) with -inf: the start value of the column maxima that an epilogue folds into it.
 __global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* __restrict__ m, int64_t n) {
   for (int64_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) m[i] = -INFINITY;
+}
+
+// Self-test of the failure path every kernel of this library shares: warp 1 waits on an mbarrier on which
+// nobody ever arrives, with a wait limit of `limit_cycles`; the wait gives up, raises the CTA's abort flag and
+// writes its code to the status word; warp 0, waiting on a second barrier with the long production limit,
+// sees the flag and leaves too; both warps meet at the final barrier and the kernel returns.  Nothing traps and
+// nothing spins without a bound.
+__global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t never[2];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(&never[0], 1);
+    mbar_init(&never[1], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const AbortCtl ctl{abort_flag, status};
+  const int warp = threadIdx.x >> 5;
+  if (warp == 1) {
+    mbar_wait_warp(&never[0], 0, ctl, STATUS_TIMEOUT_SETUP, limit_cycles);
+  } else {
+    mbar_wait_warp(&never[1], 0, ctl, STATUS_TIMEOUT_EPILOGUE);
+  }
+  __syncthreads();
 }
 
 // ----------------------------------------------------------------------------- driver entry point for tensor maps
@@ -148,9 +178,27 @@ static int64_t round_up4(int64_t v) { return (v + 3) & ~int64_t(3); }
 
 // ----------------------------------------------------------------------------- lm2exp launch
 
+// `after_prepass`: the stabiliser pre-pass was launched just before on the same stream; the kernel is then
+// launched as its programmatic dependent (its threads wait for the pre-pass before they read m).
+template <class Kern, class... Args>
+static int launch_maybe_dependent(Kern kern, int grid, int threads, int smem, cudaStream_t stream, bool after_prepass,
+                                  Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = after_prepass ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+}
+
 template <class Cfg>
 static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, Lm2expParams p,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, bool after_prepass) {
   auto kern = lm2exp_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -167,8 +215,7 @@ static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, to, p);
-  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+  return launch_maybe_dependent(kern, grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb, to, p);
 }
 
 //                          BN   MT PREC NS
@@ -189,7 +236,7 @@ using LmPairX = Lm2expPairCfg<1, 3>;
 // Launch on CTA pairs: a cluster of two CTAs per 256 x 256 tile.
 template <class Cfg>
 static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, Lm2expParams p,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, bool after_prepass) {
   auto kern = lm2exp_pair_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -223,8 +270,35 @@ static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, cons
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int clusters = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
-  kern<<<2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, to, p);
-  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+  return launch_maybe_dependent(kern, 2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb, to,
+                                p);
+}
+
+using LmTsPair = Lm2expTsPairCfg<8, 4>;
+
+// The CTA-pair kernel with the generated operand in tensor memory (plain TF32, a with j contiguous).
+static int launch_lm2exp_tspair(const CUtensorMap& ta, const CUtensorMap& tb_plain, const CUtensorMap& to,
+                                Lm2expParams p, cudaStream_t stream, bool after_prepass) {
+  using Cfg = LmTsPair;
+  auto kern = lm2exp_tspair_kernel<Cfg>;
+  static std::once_flag once[64];
+  static cudaError_t attr_rc[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return TRITURUS_B200_ELAUNCH;
+  std::call_once(once[dev], [&] {
+    attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  });
+  if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  p.tiles_m = (p.I + Cfg::BN - 1) / Cfg::BN;
+  p.tiles_n = (p.K + 2 * Cfg::BM - 1) / (2 * Cfg::BM);
+  const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
+  if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
+  p.num_tiles = static_cast<int>(nt);
+  const int max_clusters = sm_count() / 2;  // one CTA per SM (shared memory and all of TMEM), pairs on SM pairs
+  const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
+  return launch_maybe_dependent(kern, 2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb_plain,
+                                to, p);
 }
 
 static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt) {
@@ -265,6 +339,7 @@ static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256,
 struct Lm2expPlan {
   int bn, mt;   // output columns per tile, 128-row blocks per CTA
   bool pair;    // 256 x 256 tile on a pair of CTAs
+  bool tspair;  // ... by the kernel that keeps the generated operand in tensor memory (variant 2566)
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
   bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
   bool promote_tf32;      // plain TF32 over more than kLongContraction terms: accumulator re-summed in chunks
@@ -294,6 +369,11 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
+  const bool tspair = tile_variant == 2566;
+  if (tspair) {
+    if (precision != TRITURUS_B200_PRECISION_TF32) return TRITURUS_B200_EINVAL;
+    tile_variant = 2564;  // same tile and stabiliser handling as the other CTA-pair kernel
+  }
   int bn = tile_variant / 10;
   const int mt = tile_variant % 10;
   const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
@@ -311,6 +391,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   out->bn = bn;
   out->mt = pair ? 4 : mt;
   out->pair = pair;
+  out->tspair = tspair;
   out->fused = fused && !have_m;
   out->colmax_exclusive = !pair && I <= 128 * mt;
   out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
@@ -322,6 +403,13 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
 using namespace tb200;
 
 extern "C" {
+
+#ifdef TB200_TIMELINE
+// Development builds only: copy the timeline of the last launch of the TMEM-operand pair kernel to the host.
+int triturus_b200_debug_timeline(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, tb200::g_timeline, sizeof(long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int triturus_b200_version(void) { return 100; }
 
@@ -342,6 +430,13 @@ const char* triturus_b200_strerror(int code) {
     case STATUS_TIMEOUT_SETUP: return "device: setup wait timed out";
     default: return "unknown code";
   }
+}
+
+int triturus_b200_selftest_wait_timeout(int32_t* status_dev, int64_t limit_cycles, void* stream) {
+  // at most ~0.1 s of spinning: this is a test of the error path, not a way to occupy a GPU
+  if (status_dev == nullptr || limit_cycles < 1000 || limit_cycles > 200000000LL) return TRITURUS_B200_EINVAL;
+  wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status_dev, limit_cycles);
+  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
@@ -370,6 +465,16 @@ int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, in
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
   return plan.fused ? 1 : 2;
+}
+
+int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
+  if (R <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  Lm2expPlan plan;
+  const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
+  if (rc != TRITURUS_B200_OK) return rc;
+  return (plan.fused ? 2 : 1) * 100000 + plan.bn * 10 + (plan.tspair ? 6 : plan.mt);
 }
 
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K) {
@@ -436,11 +541,9 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
     const int64_t blocks = (n + 255) / 256;
     fill_neg_inf_kernel<<<static_cast<int>(blocks < 1184 ? blocks : 1184), 256, 0, st>>>(out_colmax, n);
   }
-  if (!fused && b_colmax == nullptr) {
-    const int64_t bstr[3] = {bs0, bs1, 1};
-    rc = triturus_b200_colmax_f32(b, static_cast<float*>(workspace), R, J, K, bstr, stream);
-    if (rc != TRITURUS_B200_OK) return rc;
-  }
+  // Every tensor map is encoded before the pre-pass is launched: the contraction kernel then follows it
+  // directly in the stream, which its launch as a programmatic dependent requires.
+  const bool prepass = !fused && b_colmax == nullptr;
 
   CUtensorMap ta, tb;
   if (a_mn) {
@@ -494,17 +597,37 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
   p.fused_max = fused ? 1 : 0;
   p.status = status_dev;
 
+  // The TMEM-operand pair kernel takes a with j contiguous and does not fold column maxima of the result; other
+  // calls run on the pair kernel that keeps the operand in shared memory.  Its b tiles are 32 rows j x 128
+  // columns k, unswizzled (only the transform threads read them).
+  const bool use_ts = plan.tspair && !a_mn && out_colmax == nullptr;
+  CUtensorMap tb_plain;
+  if (use_ts) {
+    const int64_t dims[3] = {K, J, R};
+    const int64_t strides[3] = {1, bs1, bs0};
+    const uint32_t box[3] = {128, 32, 1};
+    rc = make_tmap(&tb_plain, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  if (prepass) {
+    const int64_t bstr[3] = {bs0, bs1, 1};
+    rc = triturus_b200_colmax_f32(b, static_cast<float*>(workspace), R, J, K, bstr, stream);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  const bool dep = prepass;
+  if (use_ts) return launch_lm2exp_tspair(ta, tb_plain, to, p, st, dep);
   if (pair) {
-    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st)
-                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st);
+    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st, dep)
+                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st, dep);
   }
   if (precision == TRITURUS_B200_PRECISION_3XTF32) {
-    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmX_128_1>(ta, tb, to, p, st);
+    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmX_128_1>(ta, tb, to, p, st, dep);
   }
-  if (bn == 256) return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st);
+  if (bn == 256)
+    return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st, dep);
   if (plan.promote_tf32)
-    return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmP_128_1>(ta, tb, to, p, st);
-  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st);
+    return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmP_128_1>(ta, tb, to, p, st, dep);
+  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st, dep);
 }
 
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
@@ -541,33 +664,49 @@ int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t
 
 namespace tb200 {
 
-// Slices per tile for the contraction split: enough work items to cover the SMs, each slice at least
-// kMinSliceBlocks k-blocks long so the pipeline fill and the per-item column maxima stay a small part.
-// The i range is cut first (a transform thread keeps its exp(b) registers across a whole i range).
+// How the contraction of a launch is shared out (see LtWork in lt2exp_kernel.cuh).
 struct LtSplit {
-  int split_i, split_j;
+  int nsplit;  // equal slices per tile, one work item each (1: whole tiles)
+  int stream;  // 1: every CTA gets the same number of k-blocks of the whole launch, across tile borders
 };
 
+// request: 0 = automatic, 1 = never split (deterministic), 9999 = automatic but split in any case,
+// 9998 = stream, anything else = that many slices per tile.
+//  * Few tiles (they would occupy at most half the SMs): slices, enough to cover the SMs, each at least
+//    kMinSliceBlocks k-blocks long so the pipeline fill and the per-item column maxima stay a small part.
+//  * A last wave that is less than 90 % full on a contraction of at least kMinStreamBlocks k-blocks per tile:
+//    stream, which keeps every SM busy to the end (R = 8 entries of 256 x 4096 results on 256 x 256 tiles are
+//    128 tiles on 148 SMs: 0.86 of a wave).  The two extra launches (zero fill, log pass) and the additions
+//    into the result cost about as much as 50 k-blocks per tile, hence the minimum length.
 static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
   constexpr int kMinSliceBlocks = 16;
+  constexpr int kMinStreamBlocks = 256;
   const int JC = (J + 31) / 32;
   const int64_t kb = static_cast<int64_t>(JC) * I;
+  const int sms = sm_count();
+  LtSplit sp{1, 0};
+  if (request == 1) return sp;
+  if (request == 9998) {
+    sp.stream = 1;
+    return sp;
+  }
   int64_t want = request;
-  if (request == 0 || request == 9999) {  // automatic; 9999: automatic, but at least two slices
-    const int sms = sm_count();
+  if (request == 0 || request == 9999) {
     want = tiles * 2 > sms ? 1 : sms / tiles;
     // Two more launches (zero-fill and log pass) cost about as much as 50 k-blocks of the main loop: a
     // contraction shorter than that is left whole.
     if (request == 0 && kb < 64) want = 1;
     if (request == 9999 && want < 2) want = 2;
+    if (want == 1 && tiles > sms / 2) {
+      const int64_t waves = (tiles + sms - 1) / sms;
+      const bool ragged = tiles * 10 < waves * sms * 9;  // last wave under 90 % full
+      if (ragged && kb >= kMinStreamBlocks && waves <= 8) sp.stream = 1;
+      return sp;
+    }
   }
   if (want > kb / kMinSliceBlocks) want = kb / kMinSliceBlocks;
   if (want < 1) want = 1;
-  LtSplit sp;
-  sp.split_i = static_cast<int>(want < I / 8 ? want : (I / 8 > 0 ? I / 8 : 1));
-  int64_t sj = want / sp.split_i;
-  if (sj > JC) sj = JC;
-  sp.split_j = static_cast<int>(sj < 1 ? 1 : sj);
+  sp.nsplit = static_cast<int>(want);
   return sp;
 }
 
@@ -586,14 +725,17 @@ static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, int split_r
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const LtSplit sp = lt2exp_split(nt, p.I, p.J, split_request);
-  p.split_i = sp.split_i;
-  p.split_j = sp.split_j;
-  const int64_t items = nt * sp.split_i * sp.split_j;
+  p.nsplit = sp.nsplit;
+  p.stream = sp.stream;
+  const int64_t items = nt * sp.nsplit;
   if (items > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_items = static_cast<int>(items);
-  const bool split = sp.split_i * sp.split_j > 1;
+  const bool split = sp.nsplit > 1 || sp.stream != 0;
+  // the log pass of a split launch runs on a (K / 128, S / 64, R) grid
+  if (split && (p.S + 63) / 64 > 65535) return TRITURUS_B200_EINVAL;
   if (launches_only != nullptr) {
-    *launches_only = split ? 3 : 1;
+    // query only: launches in the low digit, the split code above it
+    *launches_only = (split ? 3 : 1) + 10 * (sp.stream ? 9998 : sp.nsplit);
     return TRITURUS_B200_OK;
   }
   std::call_once(once[dev], [&] {
@@ -606,11 +748,10 @@ static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, int split_r
     lt2exp_zero_kernel<<<static_cast<int>(zb < 4 * sm_count() ? zb : 4 * sm_count()), 256, 0, stream>>>(
         p.out, p.out_s0, p.out_s1, p.R, p.S, p.K);
   }
-  const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
+  const int grid = (sp.stream || p.num_items >= sm_count()) ? sm_count() : p.num_items;
   kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tw, p);
   if (split) {
     const dim3 fgrid((p.K + 127) / 128, (p.S + 63) / 64, p.R);
-    if (fgrid.y > 65535u) return TRITURUS_B200_EINVAL;
     if (Cfg::PREC) lt2exp_finish_kernel<1><<<fgrid, 256, 0, stream>>>(p);
     else lt2exp_finish_kernel<0><<<fgrid, 256, 0, stream>>>(p);
   }
@@ -667,6 +808,8 @@ static int lt2exp_variant(int variant, int precision, int64_t R, int64_t S, int6
   }
   *bn = tile / 10;
   *mt = tile % 10;
+  // 3xTF32 keeps hi and lo copies of both operands: two row blocks leave room for 128 columns only
+  if (precision == TRITURUS_B200_PRECISION_3XTF32 && *bn == 256 && *mt == 2) *bn = 128;
   *promote = long_tf && (tile == 1281 || tile == 1282 || tile == 2561);
   // operand in TMEM: 128 columns x 128 / 256 rows (1283 / 1284), 256 columns x 128 rows (1285)
   if (*bn == 128 && (*mt == 3 || *mt == 4 || *mt == 5)) return TRITURUS_B200_OK;
@@ -703,8 +846,8 @@ static int lt2exp_dispatch(int precision, int bn, int mt, bool promote, Args... 
   return mt == 2 ? launch_lt2exp<LtT_128_2>(args...) : launch_lt2exp<LtT_128_1>(args...);
 }
 
-extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
-                                             int variant) {
+static int lt2exp_query(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant,
+                        bool want_plan) {
   int rc = lt2exp_check_dims(R, S, I, J, K, precision);
   if (rc != TRITURUS_B200_OK) return rc;
   int bn, mt, split;
@@ -720,7 +863,18 @@ extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, in
   int n = 0;
   CUtensorMap none{};
   rc = lt2exp_dispatch(precision, bn, mt, promote, none, p, split, static_cast<cudaStream_t>(nullptr), &n);
-  return rc == TRITURUS_B200_OK ? n : rc;
+  if (rc != TRITURUS_B200_OK) return rc;
+  return want_plan ? (n / 10) * 10000 + bn * 10 + mt : n % 10;
+}
+
+extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
+                                             int variant) {
+  return lt2exp_query(R, S, I, J, K, precision, variant, false);
+}
+
+extern "C" int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
+                                         int variant) {
+  return lt2exp_query(R, S, I, J, K, precision, variant, true);
 }
 
 // Shared body of the lt2exp entry points.  a_colmax / b_colmax (optional, both or neither): [R, K] column

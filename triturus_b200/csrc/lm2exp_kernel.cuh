@@ -474,6 +474,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int tt = threadIdx.x - 8 * 32;
     uint32_t it = 0, tcount = 0, max_passes = 0;
     bool ok = true;
+    if (!fused) pdl_wait();  // m comes from the pre-pass, which may still be running when this kernel starts
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);

@@ -213,6 +213,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int q = warp & 3;
     uint8_t* stg = epi_stage + q * 4096;
     const bool use_tma = p.out_tma != 0;
+    pdl_wait();  // m comes from the pre-pass, which may still be running when this kernel starts
     uint32_t tcount = 0, nblk = 0;  // tiles seen; staging boxes handed to the fold warp so far
     bool ok = true;
     const bool emit_max = p.out_max != nullptr;
@@ -350,6 +351,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int tt = threadIdx.x - 8 * 32;
     uint32_t it = 0;
     bool ok = true;
+    pdl_wait();  // m comes from the pre-pass (the producer warp is already loading operand tiles meanwhile)
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
       int r, n0, i0;
       decode(tile, r, n0, i0);

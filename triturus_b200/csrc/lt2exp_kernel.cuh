@@ -19,9 +19,11 @@
 //               The NTT / BN thread groups take alternate k-blocks.
 //
 // Contraction split.  A shape with few output tiles (small batch, S and K) would leave most SMs idle while
-// each busy one walks the whole (i, j) range.  The launcher can therefore cut the contraction of every tile
-// into split_j * split_i slices, one work item each.  All slices of a tile use the same stabilisers (the
-// column maxima are taken over the full I and J), so their accumulators add linearly: in split mode the
+// each busy one walks the whole (i, j) range, and a tile count that is not a multiple of the SM count leaves
+// the last wave partly empty.  The launcher can therefore cut the contraction of every tile into nsplit equal
+// slices, one work item each, or (stream) lay the k-blocks of all tiles end to end and give every CTA the
+// same length of that line, whatever tiles it crosses.  All parts of a tile use the same stabilisers (the
+// column maxima are taken over the full I and J), so their accumulators add linearly: in these modes the
 // epilogue adds its raw accumulator into the zero-filled output with red.global.add and
 // lt2exp_finish_kernel then turns the sums into (ma + mb) + log(sum) in place.
 //
@@ -47,8 +49,9 @@ struct Lt2expParams {
   int64_t out_s0, out_s1;
   int R, S, I, J, K;
   int tiles_m, tiles_n, num_tiles;
-  int split_i, split_j;  // slices of the i range and of the j-chunk range per tile (1, 1: no split)
-  int num_items;         // num_tiles * split_i * split_j
+  int nsplit;     // equal slices of the contraction per tile (1: whole tiles)
+  int stream;     // 1: the k-blocks of all tiles form one line that the CTAs share out evenly (see LtWork)
+  int num_items;  // num_tiles * nsplit (not used when stream == 1)
   int vec_ab;            // a and b allow 16-byte loads along k (alignment, strides and K multiples of 4)
   int* status;
   // Chains of layers (all optional, contiguous [R, K]): column maxima of a and of b supplied by the caller
@@ -59,6 +62,66 @@ struct Lt2expParams {
   const float* mb_in;
   float* out_max;
 };
+
+// One work item: the k-blocks [kb_lo, kb_hi) of output tile `tile`.  k-block index = jc * I + i, so a range
+// is whole rows of the (jc, i) grid plus a partial first and last row.
+struct LtItem {
+  int tile, kb_lo, kb_hi;
+};
+
+// The work items of one CTA, in the order every role of the CTA walks them.
+//  * stream == 0: item q = tile * nsplit + slice, slices of equal length, items taken round robin over the CTAs;
+//  * stream == 1: the num_tiles * kb_tile k-blocks of the launch form one line, cut into gridDim.x ranges of
+//    equal length (cuts on multiples of 8 k-blocks); a CTA walks its range tile by tile.
+struct LtWork {
+  int64_t pos, end;
+  int q, nq, step;
+  int kb_tile, nsplit, stream;
+  __device__ LtWork(const Lt2expParams& p, int kb_tile_) {
+    kb_tile = kb_tile_;
+    nsplit = p.nsplit;
+    stream = p.stream;
+    q = blockIdx.x;
+    nq = p.num_items;
+    step = gridDim.x;
+    pos = end = 0;
+    if (stream) {
+      const int64_t total = static_cast<int64_t>(p.num_tiles) * kb_tile;
+      const int64_t g = gridDim.x, c = blockIdx.x;
+      pos = c == 0 ? 0 : ((total * c / g) & ~int64_t(7));
+      end = c == g - 1 ? total : ((total * (c + 1) / g) & ~int64_t(7));
+    }
+  }
+  __device__ bool next(LtItem& w) {
+    if (stream) {
+      if (pos >= end) return false;
+      const int64_t tile = pos / kb_tile;
+      w.tile = static_cast<int>(tile);
+      w.kb_lo = static_cast<int>(pos - tile * kb_tile);
+      const int64_t len = end - pos;
+      w.kb_hi = (len < kb_tile - w.kb_lo) ? w.kb_lo + static_cast<int>(len) : kb_tile;
+      pos += w.kb_hi - w.kb_lo;
+      return true;
+    }
+    if (q >= nq) return false;
+    w.tile = q / nsplit;
+    const int sl = q - w.tile * nsplit;
+    w.kb_lo = static_cast<int>(static_cast<int64_t>(sl) * kb_tile / nsplit);
+    w.kb_hi = static_cast<int>(static_cast<int64_t>(sl + 1) * kb_tile / nsplit);
+    q += step;
+    return true;
+  }
+};
+
+// Rows i of j-chunk jc that belong to the item: [lt_row_lo, lt_row_hi).
+__device__ __forceinline__ int lt_row_lo(const LtItem& w, int jc, int I) {
+  const int lo = w.kb_lo - jc * I;
+  return lo > 0 ? lo : 0;
+}
+__device__ __forceinline__ int lt_row_hi(const LtItem& w, int jc, int I) {
+  const int hi = w.kb_hi - jc * I;
+  return hi < I ? hi : I;
+}
 
 template <int BN_, int MT_, int PREC_, int NS_, int NTW_, bool PROMOTE_ = (PREC_ != 0)>
 struct Lt2expCfg {
@@ -196,29 +259,17 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
   const uint32_t tmem_base = *tmem_slot;
 
   const int JC = (p.J + BK - 1) / BK;  // j-chunks; the k-blocks of a work item are (jc, i), i fastest
-  const int nsplit = p.split_i * p.split_j;
-  const bool split_mode = nsplit > 1;
+  const int KBT = JC * p.I;            // k-blocks per output tile
+  const bool split_mode = p.nsplit > 1 || p.stream != 0;  // partial sums are added into the zero-filled output
 
-  // Work item -> output tile (r, n0, s0) and contraction slice [jc_lo, jc_hi) x [i_lo, i_hi).
-  struct Slice {
-    int jc_lo, jc_hi, i_lo, i_hi;
-  };
-  auto decode = [&](int item, int& r, int& n0, int& s0) -> Slice {
-    const int tile = item / nsplit;
-    const int sp = item - tile * nsplit;
-    const int pj = sp / p.split_i, pi = sp - pj * p.split_i;
-    Slice sl;
-    sl.jc_lo = static_cast<int>(static_cast<int64_t>(pj) * JC / p.split_j);
-    sl.jc_hi = static_cast<int>(static_cast<int64_t>(pj + 1) * JC / p.split_j);
-    sl.i_lo = static_cast<int>(static_cast<int64_t>(pi) * p.I / p.split_i);
-    sl.i_hi = static_cast<int>(static_cast<int64_t>(pi + 1) * p.I / p.split_i);
+  // Output tile -> (r, n0 = first column, s0 = first row).
+  auto decode = [&](int tile, int& r, int& n0, int& s0) {
     const int tm = tile % p.tiles_m;
     const int rest = tile / p.tiles_m;
     const int tn = rest % p.tiles_n;
     r = rest / p.tiles_n;
     n0 = tn * BN;
     s0 = tm * (BM * MT);
-    return sl;
   };
 
   if (warp == 0) {
@@ -226,11 +277,13 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      LtWork work(p, KBT);
+      for (LtItem w; ok && work.next(w);) {
         int r, n0, s0;
-        const Slice sl = decode(item, r, n0, s0);
-        for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
-          for (int i = sl.i_lo; i < sl.i_hi; ++i, ++it) {
+        decode(w.tile, r, n0, s0);
+        for (int jc = w.kb_lo / p.I; ok && jc * p.I < w.kb_hi; ++jc) {
+          const int i_hi = lt_row_hi(w, jc, p.I);
+          for (int i = lt_row_lo(w, jc, p.I); i < i_hi; ++i, ++it) {
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
@@ -249,10 +302,9 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       constexpr uint32_t idesc = umma_idesc_tf32(BM, BN);
       uint32_t it = 0, ccount = 0;  // k-blocks and accumulation chunks issued so far
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-        int r, n0, s0;
-        const Slice sl = decode(item, r, n0, s0);
-        const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
+      LtWork work(p, KBT);
+      for (LtItem w; ok && work.next(w);) {
+        const int KB = w.kb_hi - w.kb_lo;
         const int nch = Cfg::PROMOTE ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
         int kb = 0;
         for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
@@ -302,10 +354,11 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     uint32_t tcount = 0, ccount = 0;
     bool ok = true;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+    LtWork work(p, KBT);
+    for (LtItem w; ok && work.next(w); ++tcount) {
       int r, n0, s0;
-      const Slice sl = decode(item, r, n0, s0);
-      const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
+      decode(w.tile, r, n0, s0);
+      const int KB = w.kb_hi - w.kb_lo;
       const int nch = Cfg::PROMOTE ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
       const int slot = tcount & 1;
       for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
@@ -412,10 +465,10 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
     const int grp = tt / BN;     // this thread's group takes k-blocks with i % NGROUPS == grp
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+    LtWork work(p, KBT);
+    for (LtItem w; ok && work.next(w); ++tcount) {
       int r, n0, s0;
-      const Slice sl = decode(item, r, n0, s0);
-      const int In = sl.i_hi - sl.i_lo;
+      decode(w.tile, r, n0, s0);
       const int kcol = n0 + n;
       const bool col_ok = kcol < p.K;
       const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
@@ -467,8 +520,10 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
         msum[slot * BN + n] = ma + mb;
       }
 
-      const float* a_sl = a_col + static_cast<int64_t>(sl.i_lo) * p.a_s1;  // first row of this slice
-      for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
+      for (int jc = w.kb_lo / p.I; ok && jc * p.I < w.kb_hi; ++jc) {
+        const int i_lo = lt_row_lo(w, jc, p.I);
+        const int In = lt_row_hi(w, jc, p.I) - i_lo;                             // rows of this j-chunk in the item
+        const float* a_sl = a_col + static_cast<int64_t>(i_lo) * p.a_s1;  // the first of them
         // exp(b - mb) for this thread's column and the 32 j of the chunk; zero past J or K.
         // All 32 loads are issued before the first exp: padding reads as -inf, which exp turns into an exact
         // zero, so no exp sits behind a branch.
@@ -500,7 +555,7 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
           for (int x = 0; x < PF; ++x) {
             const int i = ib + grp + x * NG;
             if (i >= In) break;
-            const uint32_t my_it = it + static_cast<uint32_t>(i);  // k-block index of (jc, i_lo + i)
+            const uint32_t my_it = it + static_cast<uint32_t>(i);  // stage counter of k-block (jc, i_lo + i)
             const int s = my_it % NS;
             const uint32_t ph = (my_it / NS) & 1;
             if (!(ok = mbar_wait_warp(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;

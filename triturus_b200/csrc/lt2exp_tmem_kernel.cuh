@@ -111,29 +111,17 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
   const uint32_t tmem_base = *tmem_slot;
 
   const int JC = (p.J + BK - 1) / BK;
-  const int nsplit = p.split_i * p.split_j;
-  const bool split_mode = nsplit > 1;
+  const int KBT = JC * p.I;  // k-blocks per output tile
+  const bool split_mode = p.nsplit > 1 || p.stream != 0;
 
-  struct Slice {
-    int jc_lo, jc_hi, i_lo, i_hi;
-  };
-  // Work item -> output tile (r, n0 = first column k, s0 = first row s) and contraction slice.
-  auto decode = [&](int item, int& r, int& n0, int& s0) -> Slice {
-    const int tile = item / nsplit;
-    const int sp = item - tile * nsplit;
-    const int pj = sp / p.split_i, pi = sp - pj * p.split_i;
-    Slice sl;
-    sl.jc_lo = static_cast<int>(static_cast<int64_t>(pj) * JC / p.split_j);
-    sl.jc_hi = static_cast<int>(static_cast<int64_t>(pj + 1) * JC / p.split_j);
-    sl.i_lo = static_cast<int>(static_cast<int64_t>(pi) * p.I / p.split_i);
-    sl.i_hi = static_cast<int>(static_cast<int64_t>(pi + 1) * p.I / p.split_i);
+  // Output tile -> (r, n0 = first column k, s0 = first row s); the items of a CTA come from LtWork.
+  auto decode = [&](int tile, int& r, int& n0, int& s0) {
     const int tm = tile % p.tiles_m;
     const int rest = tile / p.tiles_m;
     const int tn = rest % p.tiles_n;
     r = rest / p.tiles_n;
     n0 = tn * BN;
     s0 = tm * (BM * MT);
-    return sl;
   };
 
   if (warp == 0) {
@@ -141,11 +129,13 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      LtWork work(p, KBT);
+      for (LtItem w; ok && work.next(w);) {
         int r, n0, s0;
-        const Slice sl = decode(item, r, n0, s0);
-        for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
-          for (int i = sl.i_lo; i < sl.i_hi; ++i, ++it) {
+        decode(w.tile, r, n0, s0);
+        for (int jc = w.kb_lo / p.I; ok && jc * p.I < w.kb_hi; ++jc) {
+          const int i_hi = lt_row_hi(w, jc, p.I);
+          for (int i = lt_row_lo(w, jc, p.I); i < i_hi; ++i, ++it) {
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&opnd_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
@@ -172,10 +162,9 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
       int s = 0;
       uint32_t ph = 0;
       bool ok = true, ready = false;
-      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
-        int r, n0, s0;
-        const Slice sl = decode(item, r, n0, s0);
-        const int KB = (sl.jc_hi - sl.jc_lo) * (sl.i_hi - sl.i_lo);
+      LtWork work(p, KBT);
+      for (LtItem w; ok && work.next(w); ++tcount) {
+        const int KB = w.kb_hi - w.kb_lo;
         const int buf = tcount % Cfg::NBUF;
         const uint32_t aph = (tcount / Cfg::NBUF) & 1;
         if (!(ok = mbar_wait_warp(&acc_empty[buf], aph ^ 1, ctl, STATUS_TIMEOUT_MMA))) break;
@@ -215,9 +204,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+    LtWork work(p, KBT);
+    for (LtItem w; ok && work.next(w); ++tcount) {
       int r, n0, s0;
-      decode(item, r, n0, s0);
+      decode(w.tile, r, n0, s0);
       const int buf = tcount % Cfg::NBUF;
       const uint32_t aph = (tcount / Cfg::NBUF) & 1;
       const int slot = tcount & 1;
@@ -293,10 +283,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
                                (Cfg::NB == 2 ? static_cast<uint32_t>((tt / 128) * BK) : 0u);
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++tcount) {
+    LtWork work(p, KBT);
+    for (LtItem w; ok && work.next(w); ++tcount) {
       int r, n0, s0;
-      const Slice sl = decode(item, r, n0, s0);
-      const int In = sl.i_hi - sl.i_lo;
+      decode(w.tile, r, n0, s0);
       const int kcol = n0 + n;
       const bool col_ok = kcol < p.K;
       const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
@@ -345,8 +335,10 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
         msum[slot * BN + n] = ma + mb;
       }
 
-      const float* a_sl = a_col + static_cast<int64_t>(sl.i_lo) * p.a_s1;
-      for (int jc = sl.jc_lo; ok && jc < sl.jc_hi; ++jc) {
+      for (int jc = w.kb_lo / p.I; ok && jc * p.I < w.kb_hi; ++jc) {
+        const int i_lo = lt_row_lo(w, jc, p.I);
+        const int In = lt_row_hi(w, jc, p.I) - i_lo;  // rows of this j-chunk in the item
+        const float* a_sl = a_col + static_cast<int64_t>(i_lo) * p.a_s1;
         // exp(b - mb) of the 32 j of the chunk; padding (past J or K) enters the exp as -inf: exact zero.
         float eb[32];
 #pragma unroll

@@ -90,8 +90,10 @@ __device__ __forceinline__ void raise_abort(const AbortCtl& ctl, int code) {
   if (ctl.status != nullptr) atomicCAS(ctl.status, 0, code);
 }
 
-// Bounded wait on one phase of an mbarrier.  Returns false if the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code) {
+// Bounded wait on one phase of an mbarrier.  Returns false if the CTA is aborting.  `limit` is the number of
+// clock cycles after which the wait gives up (the kernels use WAIT_LIMIT_CYCLES; the self-test passes a short one).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code,
+                                          long long limit = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -100,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*ctl.flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       raise_abort(ctl, code);
       return false;
     }
@@ -108,8 +110,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // Same wait, made warp-uniform: either every lane sees the phase complete or every lane leaves.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code) {
-  const bool ok = mbar_wait(bar, parity, ctl, code);
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const AbortCtl& ctl, int code,
+                                               long long limit = WAIT_LIMIT_CYCLES) {
+  const bool ok = mbar_wait(bar, parity, ctl, code, limit);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -140,6 +143,16 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+
+// ----------------------------------------------------------------------------- programmatic dependent launch
+//
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the kernel before
+// it in the stream is still running, once every block of that kernel has called pdl_launch_dependents() or
+// exited.  Its threads must call pdl_wait() before they touch anything the earlier kernel writes; the call
+// returns when that kernel has completed and its writes are visible.  Both are no-ops in a kernel launched the
+// ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------- fences
 
