@@ -108,10 +108,10 @@ int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, i
  *            counterpart of the reference's NUM_SPLITS and mode argument (triturus/lt2exp.py:533-541):
  *            0 = automatic (slices when the output tiles would occupy fewer than half the SMs; when the last
  *            wave of tiles would be less than 90 % full and a tile's contraction is at least 8192 terms long,
- *            the k-blocks of all tiles are laid end to end and every CTA takes the same length of that line,
- *            across tile borders), 1 = never (mode "unsplit"), n >= 2 = n slices (fewer if a slice would drop
- *            below 16 k-blocks), 9998 = the end-to-end form in any case, 9999 = as automatic but at least two
- *            slices (mode "split").  Plain TF32 over more than 32768 terms re-sums its accumulator every 4096
+ *            the full waves run as whole tiles and the contractions of the last wave's tiles are shared among
+ *            all SMs), 1 = never (mode "unsplit"), n >= 2 = n slices (fewer if a slice would drop below 16
+ *            k-blocks), 9998 = the shared last wave in any case, 9999 = as automatic but at least two slices
+ *            (mode "split").  Plain TF32 over more than 32768 terms re-sums its accumulator every 4096
  *            terms with rounded adds (automatic tiles only leave room for that; an explicit 2562 / 128x tile is
  *            honoured and runs without).  A split call launches three kernels: zero-fill
  *            of out, the slices adding their partial sums into out with fp32 reductions (so the last bits
@@ -123,8 +123,8 @@ int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, i
  * (1, or 3 when the contraction is split); negative on invalid arguments. */
 int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
 /* What a triturus_b200_lt2exp_f32 call with these arguments runs on the current device, as the explicit variant
- * code that pins it: SPLIT * 10000 + BN * 10 + MT with SPLIT = 1 (whole tiles), the slice count, or 9998 (end to
- * end).  The counterpart of reading the reference's autotuner choice (triturus/lt2exp.py:9-75,78-222); negative
+ * code that pins it: SPLIT * 10000 + BN * 10 + MT with SPLIT = 1 (whole tiles), the slice count, or 9998 (last
+ * wave shared).  The counterpart of reading the reference's autotuner choice (triturus/lt2exp.py:9-75,78-222); negative
  * on invalid arguments. */
 int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
 /* The same for triturus_b200_lm2exp_f32: STAB * 100000 + BN * 10 + MT with STAB = 1 (pre-pass) or 2 (fused max
@@ -134,6 +134,28 @@ int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, flo
                              int64_t I, int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
                              const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
                              int32_t* status_dev, void* stream);
+/*
+ * The same with caller-provided scratch memory, the counterpart of the lock tensor the reference's wrapper
+ * allocates for its split kernel (triturus/lt2exp.py:555-562).  With it the shared last wave (SPLIT 9998, and the
+ * automatic choice for a ragged last wave) needs one launch and no atomics: a CTA that works on a later part of
+ * a tile's contraction parks its raw partial sums in the workspace, and the CTA that holds the tile's first
+ * k-blocks adds them to its own and writes the finished results.  The order of those additions is fixed, so
+ * the results do not depend on timing.  triturus_b200_lt2exp_f32 (no workspace) never chooses the shared last
+ * wave by itself and, when asked for it, falls back to additions into the zero-filled result.
+ *   workspace: triturus_b200_lt2exp_workspace_bytes(...) bytes, 256-byte aligned (0 bytes: may be NULL); its
+ *   first 1024 bytes are cleared by a cudaMemsetAsync on `stream` in every call that uses it.  The queries
+ *   triturus_b200_lt2exp_launches / _plan describe calls of this entry point with that workspace.
+ *   The CTAs of such a launch wait for one another (with the usual bound), so the launch takes the whole GPU:
+ *   on a device that another kernel shares at the same time, a CTA may start late and a wait may run out
+ *   (reported through status_dev, never a hang).
+ */
+size_t triturus_b200_lt2exp_workspace_bytes(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
+                                            int variant);
+int triturus_b200_lt2exp_ws_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
+                                int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
+                                const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                                int precision, int variant, void* workspace, size_t workspace_bytes,
+                                int32_t* status_dev, void* stream);
 
 /*
  * lt2exp as one link of a chain of layers (see triturus_b200_lm2exp_chain_f32; the reference's kernels scan a

@@ -62,7 +62,7 @@ def test_deterministic_algorithms_switch_off_the_split():
     assert torch.equal(got, base)
 
 
-SPLITS = [2, 3, 7, 16, 64, 9998, 9999]  # 9998: k-blocks of all tiles end to end, equal share per CTA
+SPLITS = [2, 3, 7, 16, 64, 9998, 9999]  # 9998: the tiles of the last wave shared among all SMs
 
 
 @pytest.mark.parametrize("split", SPLITS)
@@ -244,9 +244,10 @@ def test_full_size_configs(name, batch, precision):
 
 @pytest.mark.parametrize("tile", [0, 1281, 1282, 2561, 2562, 1283, 1285])
 @pytest.mark.parametrize("precision", PRECISIONS)
-def test_contraction_end_to_end_ranges_cross_tiles(precision, tile):
-    """The end-to-end form on a shape where every CTA's range is longer than a tile's contraction (40 k-blocks),
-    so ranges start and end inside j-chunk rows and cover parts of two or three tiles."""
+def test_contraction_shared_last_wave(precision, tile):
+    """Whole waves plus a shared last wave on a shape with several waves of tiles (256 tiles of 128 x 128 down to 32
+    of 256 x 256 on 148 SMs): equal parts when the last wave is less than half full, mains and tails otherwise;
+    parts start and end inside j-chunk rows (a tile's contraction is 40 k-blocks of 20 rows i x 2 j-chunks)."""
     if precision == "3xtf32" and tile in (2562, 1283, 1285):
         pytest.skip("no 256 x 256 tile and no TMEM-operand kernel in 3xTF32")
     from triturus_b200 import _native
@@ -260,18 +261,39 @@ def test_contraction_end_to_end_ranges_cross_tiles(precision, tile):
     a[3, :, 77] = float("-inf")
     variant = 9998 * 10000 + tile
     prec = 0 if precision == "tf32" else 1
-    assert _native.LIB.triturus_b200_lt2exp_launches(R, S, I, J, K, prec, variant) == 3
+    # With scratch memory (what the Python wrapper passes) the kernels that build their operand in shared memory
+    # complete shared tiles in the same launch; the TMEM-operand kernels add into the zero-filled result.
+    tmem_tile = _native.LIB.triturus_b200_lt2exp_plan(R, S, I, J, K, prec, variant) % 10000 in (1283, 1284, 1285)
+    assert _native.LIB.triturus_b200_lt2exp_launches(R, S, I, J, K, prec, variant) == (3 if tmem_tile else 1)
+    assert (_native.LIB.triturus_b200_lt2exp_workspace_bytes(R, S, I, J, K, prec, variant) > 0) == (not tmem_tile)
     assert _native.LIB.triturus_b200_lt2exp_plan(R, S, I, J, K, prec, variant) // 10000 == 9998
     got = _run(w, a, b, precision=precision, variant=variant)
     want = orc.lt2exp_fp64(w, a, b)
     assert torch.all(got[3, :, 77] == float("-inf"))
     assert torch.equal(got == float("-inf"), want == float("-inf"))
     _assert_close(got, w, a, b, precision, want)
+    if not tmem_tile:
+        # parked partial sums are added in a fixed order: a second call gives the same bits
+        assert torch.equal(got, _run(w, a, b, precision=precision, variant=variant))
+        # the entry point without scratch memory runs the same ranges with additions into the result
+        import ctypes
+
+        wd, ad, bd = w.cuda(), a.cuda(), b.cuda()
+        out = torch.empty((R, S, K), device="cuda")
+        i64 = ctypes.c_int64
+        rc = _native.LIB.triturus_b200_lt2exp_f32(
+            wd.data_ptr(), ad.data_ptr(), bd.data_ptr(), out.data_ptr(), R, S, I, J, K,
+            (i64 * 4)(*wd.stride()), (i64 * 3)(*ad.stride()), (i64 * 3)(*bd.stride()), (i64 * 3)(*out.stride()),
+            prec, variant, _native._status_word(wd.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        _native.check_status()
+        _assert_close(out.cpu(), w, a, b, precision, want)
 
 
 def test_automatic_choice_balances_a_ragged_last_wave():
-    """R = 8 entries of cfg5's shape are 128 tiles of 256 x 256 on 148 SMs: the automatic choice lays the
-    contractions end to end; the full R = 64 (6.9 waves) and a deterministic call keep whole tiles."""
+    """R = 8 entries of cfg5's shape are 128 tiles of 256 x 256 on 148 SMs: the automatic choice shares the
+    contractions of that last (only) wave among all SMs; the full R = 64 (6.9 waves) and a deterministic call keep
+    whole tiles."""
     from triturus_b200 import _native
 
     plan = _native.LIB.triturus_b200_lt2exp_plan
@@ -289,7 +311,7 @@ def test_automatic_choice_balances_a_ragged_last_wave():
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_cfg5_on_the_benchmarked_tile(precision, variant):
     """cfg5's own distribution (N(-40, 15), 0.5 % -inf, I * J = 16384) on the tile the benchmarks run: 256 x 256
-    as whole tiles (12562, what the full R = 64 runs on one GPU) and with the contractions end to end (99982562,
+    as whole tiles (12562, what the full R = 64 runs on one GPU) and with the last wave shared (99982562,
     what R = 64 / N runs per GPU on 2, 4 and 8 GPUs).  The float64 oracle checks one batch entry; the whole
     result is checked for NaN, for its -inf positions and with the shift identity."""
     import triturus_b200 as tb

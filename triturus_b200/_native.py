@@ -28,6 +28,8 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lm2exp_chain_launches",
     "triturus_b200_lm2exp_chain_f32",
     "triturus_b200_lt2exp_f32",
+    "triturus_b200_lt2exp_workspace_bytes",
+    "triturus_b200_lt2exp_ws_f32",
     "triturus_b200_lt2exp_chain_f32",
     "triturus_b200_colmax_f32",
     "triturus_b200_selftest_wait_timeout",
@@ -106,6 +108,13 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.triturus_b200_lt2exp_f32.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
         i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_void_p,
+    ]  # fmt: skip
+    lib.triturus_b200_lt2exp_workspace_bytes.restype = c_size_t
+    lib.triturus_b200_lt2exp_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]
+    lib.triturus_b200_lt2exp_ws_f32.restype = c_int
+    lib.triturus_b200_lt2exp_ws_f32.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+        i64p, i64p, i64p, i64p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
     ]  # fmt: skip
     lib.triturus_b200_lt2exp_chain_f32.restype = c_int
     lib.triturus_b200_lt2exp_chain_f32.argtypes = [
@@ -329,12 +338,16 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
     b = _inner_contiguous(b)
     out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)
     with _on_device(a.device) as idx:
-        rc = LIB.triturus_b200_lt2exp_f32(
+        # scratch memory for tiles that several CTAs share (the end-to-end form of the contraction split)
+        ws_bytes = int(LIB.triturus_b200_lt2exp_workspace_bytes(R, S, I, J, K, int(precision), int(variant)))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
+        rc = LIB.triturus_b200_lt2exp_ws_f32(
             w.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(), R, S, I, J, K,
             _i64(w.stride()), _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
-            int(precision), int(variant), _status_word(a.device).data_ptr(), _raw_stream(idx),
+            int(precision), int(variant), ws.data_ptr() if ws is not None else None, ws_bytes,
+            _status_word(a.device).data_ptr(), _raw_stream(idx),
         )  # fmt: skip
-    _check(rc, "triturus_b200_lt2exp_f32")
+    _check(rc, "triturus_b200_lt2exp_ws_f32")
     return out
 
 

@@ -676,9 +676,12 @@ struct LtSplit {
 //    kMinSliceBlocks k-blocks long so the pipeline fill and the per-item column maxima stay a small part.
 //  * A last wave that is less than 90 % full on a contraction of at least kMinStreamBlocks k-blocks per tile:
 //    stream, which keeps every SM busy to the end (R = 8 entries of 256 x 4096 results on 256 x 256 tiles are
-//    128 tiles on 148 SMs: 0.86 of a wave).  The two extra launches (zero fill, log pass) and the additions
-//    into the result cost about as much as 50 k-blocks per tile, hence the minimum length.
-static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
+//    128 tiles on 148 SMs: 0.86 of a wave).  A CTA then works on up to two partial tiles besides its whole
+//    ones (prologue and epilogue of each cost about as much as 50 k-blocks), hence the minimum length.
+// auto_stream: the launch can complete shared tiles through scratch memory (see Lt2expParams::park); without
+// it the end-to-end form would have to add every partial sum into the result with atomics, which costs more
+// than the ragged wave it removes, so the automatic choice then keeps whole tiles.
+static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request, bool auto_stream) {
   constexpr int kMinSliceBlocks = 16;
   constexpr int kMinStreamBlocks = 256;
   const int JC = (J + 31) / 32;
@@ -700,7 +703,7 @@ static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
     if (want == 1 && tiles > sms / 2) {
       const int64_t waves = (tiles + sms - 1) / sms;
       const bool ragged = tiles * 10 < waves * sms * 9;  // last wave under 90 % full
-      if (ragged && kb >= kMinStreamBlocks && waves <= 8) sp.stream = 1;
+      if (auto_stream && ragged && kb >= kMinStreamBlocks && waves <= 8) sp.stream = 1;
       return sp;
     }
   }
@@ -710,9 +713,24 @@ static LtSplit lt2exp_split(int64_t tiles, int I, int J, int request) {
   return sp;
 }
 
-template <class Cfg, void (*Kern)(const CUtensorMap, const Lt2expParams)>
-static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
-                              int* launches_only) {
+// What a launch function is asked to do: launch, or (query != nullptr) only report what it would launch.
+struct LtQuery {
+  int launches;     // kernels per call
+  int split_code;   // 1 = whole tiles, n = slices per tile, 9998 = end to end
+  size_t ws_bytes;  // scratch memory the plan uses (0: none)
+};
+struct LtLaunch {
+  int split_request;
+  cudaStream_t stream;
+  LtQuery* query;   // queries assume that the caller will supply the scratch memory they report
+  void* ws;         // scratch memory of the call (may be null)
+  size_t ws_bytes;
+};
+
+constexpr size_t kParkHeader = 1024;  // flags (one int per CTA) ahead of the parked tiles
+
+template <class Cfg, void (*Kern)(const CUtensorMap, const Lt2expParams), bool CAN_PARK>
+static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, const LtLaunch& L) {
   auto kern = Kern;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -724,50 +742,95 @@ static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, int split_r
   const int64_t nt = static_cast<int64_t>(p.R) * p.tiles_m * p.tiles_n;
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
-  const LtSplit sp = lt2exp_split(nt, p.I, p.J, split_request);
+  // Scratch memory for the end-to-end form: one parked tile per CTA behind the flags.
+  const size_t park_need = kParkHeader + static_cast<size_t>(sm_count()) * Cfg::MT * Cfg::BM * Cfg::BN * sizeof(float);
+  const bool have_ws = CAN_PARK && sm_count() * sizeof(int) <= kParkHeader &&
+                       (L.query != nullptr || (L.ws != nullptr && L.ws_bytes >= park_need &&
+                                               (reinterpret_cast<uintptr_t>(L.ws) & 255) == 0));
+  const LtSplit sp = lt2exp_split(nt, p.I, p.J, L.split_request, have_ws);
   p.nsplit = sp.nsplit;
   p.stream = sp.stream;
   const int64_t items = nt * sp.nsplit;
   if (items > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_items = static_cast<int>(items);
-  const bool split = sp.nsplit > 1 || sp.stream != 0;
+  if (sp.stream) {
+    // Whole waves first, then the tiles of the last wave shared among all CTAs (LtWork in lt2exp_kernel.cuh).
+    const int G = sm_count();
+    const int64_t kbt = static_cast<int64_t>((p.J + 31) / 32) * p.I;
+    const int64_t waves = (nt + G - 1) / G;
+    p.lw_first = static_cast<int>((waves - 1) * G);
+    const int rem = static_cast<int>(nt - p.lw_first);
+    p.lw_parts = 1;
+    p.lw_main = static_cast<int>(kbt);
+    if (rem * 2 <= G) {
+      int64_t parts = G / rem;
+      if (parts > 8) parts = 8;  // shorter parts are mostly prologue and epilogue
+      if (parts > kbt) parts = kbt;
+      p.lw_parts = static_cast<int>(parts < 1 ? 1 : parts);
+    } else if (rem < G && kbt >= 2) {
+      // mains and tails: a CTA with the most tails (q of them) is busy as long as a main part, counting for
+      // every work item a prologue and epilogue worth kItemBlocks k-blocks (measured: 25 us per tail of a
+      // 256 x 256 tile against 0.73 us per k-block): q * (kbt - x + o) = x + o
+      constexpr int64_t kItemBlocks = 32;
+      const int h = G - rem;
+      const int64_t q = (rem + h - 1) / h;
+      int64_t x = ((q * (kbt + kItemBlocks) - kItemBlocks) / (q + 1)) & ~int64_t(7);
+      if (x < 1) x = 1;
+      if (x > kbt - 1) x = kbt - 1;
+      p.lw_parts = 0;
+      p.lw_main = static_cast<int>(x);
+    }
+  } else {
+    p.lw_first = p.num_tiles;
+    p.lw_parts = 1;
+    p.lw_main = 0;
+  }
+  const bool parked = sp.stream != 0 && have_ws;             // shared tiles completed through the scratch memory
+  const bool split = (sp.nsplit > 1 || sp.stream != 0) && !parked;  // ... or with additions into the zero-filled result
   // the log pass of a split launch runs on a (K / 128, S / 64, R) grid
   if (split && (p.S + 63) / 64 > 65535) return TRITURUS_B200_EINVAL;
-  if (launches_only != nullptr) {
-    // query only: launches in the low digit, the split code above it
-    *launches_only = (split ? 3 : 1) + 10 * (sp.stream ? 9998 : sp.nsplit);
+  if (L.query != nullptr) {
+    L.query->launches = split ? 3 : 1;
+    L.query->split_code = sp.stream ? 9998 : sp.nsplit;
+    L.query->ws_bytes = parked ? park_need : 0;
     return TRITURUS_B200_OK;
   }
   std::call_once(once[dev], [&] {
     attr_rc[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   });
   if (attr_rc[dev] != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  p.park = nullptr;
+  p.park_flags = nullptr;
+  if (parked) {
+    p.park_flags = static_cast<int*>(L.ws);
+    p.park = reinterpret_cast<float*>(static_cast<uint8_t*>(L.ws) + kParkHeader);
+    if (cudaMemsetAsync(L.ws, 0, kParkHeader, L.stream) != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  }
   if (split) {
     const int64_t total = static_cast<int64_t>(p.R) * p.S * p.K;
     const int64_t zb = (total + 255) / 256;
-    lt2exp_zero_kernel<<<static_cast<int>(zb < 4 * sm_count() ? zb : 4 * sm_count()), 256, 0, stream>>>(
+    lt2exp_zero_kernel<<<static_cast<int>(zb < 4 * sm_count() ? zb : 4 * sm_count()), 256, 0, L.stream>>>(
         p.out, p.out_s0, p.out_s1, p.R, p.S, p.K);
   }
   const int grid = (sp.stream || p.num_items >= sm_count()) ? sm_count() : p.num_items;
-  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream>>>(tw, p);
+  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, L.stream>>>(tw, p);
   if (split) {
     const dim3 fgrid((p.K + 127) / 128, (p.S + 63) / 64, p.R);
-    if (Cfg::PREC) lt2exp_finish_kernel<1><<<fgrid, 256, 0, stream>>>(p);
-    else lt2exp_finish_kernel<0><<<fgrid, 256, 0, stream>>>(p);
+    if (Cfg::PREC) lt2exp_finish_kernel<1><<<fgrid, 256, 0, L.stream>>>(p);
+    else lt2exp_finish_kernel<0><<<fgrid, 256, 0, L.stream>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
 template <class Cfg>
-static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
-                         int* launches_only = nullptr) {
-  return launch_lt2exp_with<Cfg, lt2exp_kernel<Cfg>>(tw, p, split_request, stream, launches_only);
+static int launch_lt2exp(const CUtensorMap& tw, Lt2expParams p, const LtLaunch& L) {
+  return launch_lt2exp_with<Cfg, lt2exp_kernel<Cfg>, true>(tw, p, L);
 }
 
+// (the kernels that keep the generated operand in tensor memory complete shared tiles with additions only)
 template <class Cfg>
-static int launch_lt2exp_tmem(const CUtensorMap& tw, Lt2expParams p, int split_request, cudaStream_t stream,
-                              int* launches_only = nullptr) {
-  return launch_lt2exp_with<Cfg, lt2exp_tmem_kernel<Cfg>>(tw, p, split_request, stream, launches_only);
+static int launch_lt2exp_tmem(const CUtensorMap& tw, Lt2expParams p, const LtLaunch& L) {
+  return launch_lt2exp_with<Cfg, lt2exp_tmem_kernel<Cfg>, false>(tw, p, L);
 }
 
 //                              MT NS   (generated operand in TMEM, 128 columns k per tile, TF32)
@@ -847,7 +910,7 @@ static int lt2exp_dispatch(int precision, int bn, int mt, bool promote, Args... 
 }
 
 static int lt2exp_query(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant,
-                        bool want_plan) {
+                        tb200::LtQuery* q, int* tile_code) {
   int rc = lt2exp_check_dims(R, S, I, J, K, precision);
   if (rc != TRITURUS_B200_OK) return rc;
   int bn, mt, split;
@@ -860,21 +923,35 @@ static int lt2exp_query(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, i
   p.I = static_cast<int>(I);
   p.J = static_cast<int>(J);
   p.K = static_cast<int>(K);
-  int n = 0;
   CUtensorMap none{};
-  rc = lt2exp_dispatch(precision, bn, mt, promote, none, p, split, static_cast<cudaStream_t>(nullptr), &n);
-  if (rc != TRITURUS_B200_OK) return rc;
-  return want_plan ? (n / 10) * 10000 + bn * 10 + mt : n % 10;
+  const tb200::LtLaunch L{split, static_cast<cudaStream_t>(nullptr), q, nullptr, 0};
+  rc = lt2exp_dispatch(precision, bn, mt, promote, none, p, L);
+  *tile_code = bn * 10 + mt;
+  return rc;
 }
 
 extern "C" int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
                                              int variant) {
-  return lt2exp_query(R, S, I, J, K, precision, variant, false);
+  tb200::LtQuery q{};
+  int tile = 0;
+  const int rc = lt2exp_query(R, S, I, J, K, precision, variant, &q, &tile);
+  return rc == TRITURUS_B200_OK ? q.launches : rc;
 }
 
 extern "C" int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision,
                                          int variant) {
-  return lt2exp_query(R, S, I, J, K, precision, variant, true);
+  tb200::LtQuery q{};
+  int tile = 0;
+  const int rc = lt2exp_query(R, S, I, J, K, precision, variant, &q, &tile);
+  return rc == TRITURUS_B200_OK ? q.split_code * 10000 + tile : rc;
+}
+
+extern "C" size_t triturus_b200_lt2exp_workspace_bytes(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K,
+                                                       int precision, int variant) {
+  tb200::LtQuery q{};
+  int tile = 0;
+  const int rc = lt2exp_query(R, S, I, J, K, precision, variant, &q, &tile);
+  return rc == TRITURUS_B200_OK ? q.ws_bytes : 0;
 }
 
 // Shared body of the lt2exp entry points.  a_colmax / b_colmax (optional, both or neither): [R, K] column
@@ -883,8 +960,8 @@ extern "C" int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_
 static int lt2exp_run(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S, int64_t I,
                       int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
                       const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
-                      const float* a_colmax, const float* b_colmax, float* out_colmax, int32_t* status_dev,
-                      void* stream) {
+                      const float* a_colmax, const float* b_colmax, float* out_colmax, void* workspace,
+                      size_t workspace_bytes, int32_t* status_dev, void* stream) {
   if ((a_colmax == nullptr) != (b_colmax == nullptr)) return TRITURUS_B200_EINVAL;
   if (out_colmax != nullptr && (out_colmax == a_colmax || out_colmax == b_colmax)) return TRITURUS_B200_EINVAL;
   if (w == nullptr || a == nullptr || b == nullptr || out == nullptr || w_strides == nullptr ||
@@ -953,8 +1030,8 @@ static int lt2exp_run(const float* w, const float* a, const float* b, float* out
                                  static_cast<cudaStream_t>(stream)>>>(out_colmax, n);
   }
 
-  return lt2exp_dispatch(precision, bn, mt, promote, tw, p, split, static_cast<cudaStream_t>(stream),
-                         static_cast<int*>(nullptr));
+  const tb200::LtLaunch L{split, static_cast<cudaStream_t>(stream), nullptr, workspace, workspace_bytes};
+  return lt2exp_dispatch(precision, bn, mt, promote, tw, p, L);
 }
 
 extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
@@ -963,7 +1040,16 @@ extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const fl
                                         const int64_t out_strides[3], int precision, int variant,
                                         int32_t* status_dev, void* stream) {
   return lt2exp_run(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision, variant,
-                    nullptr, nullptr, nullptr, status_dev, stream);
+                    nullptr, nullptr, nullptr, nullptr, 0, status_dev, stream);
+}
+
+extern "C" int triturus_b200_lt2exp_ws_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
+                                           int64_t S, int64_t I, int64_t J, int64_t K, const int64_t w_strides[4],
+                                           const int64_t a_strides[3], const int64_t b_strides[3],
+                                           const int64_t out_strides[3], int precision, int variant, void* workspace,
+                                           size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  return lt2exp_run(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision, variant,
+                    nullptr, nullptr, nullptr, workspace, workspace_bytes, status_dev, stream);
 }
 
 extern "C" int triturus_b200_lt2exp_chain_f32(const float* w, const float* a, const float* b, float* out, int64_t R,
@@ -974,7 +1060,7 @@ extern "C" int triturus_b200_lt2exp_chain_f32(const float* w, const float* a, co
                                               const float* b_colmax, float* out_colmax, int32_t* status_dev,
                                               void* stream) {
   return lt2exp_run(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision, variant,
-                    a_colmax, b_colmax, out_colmax, status_dev, stream);
+                    a_colmax, b_colmax, out_colmax, nullptr, 0, status_dev, stream);
 }
 
 // ----------------------------------------------------------------------------- lm2exp without caller scratch

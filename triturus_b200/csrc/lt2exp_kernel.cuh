@@ -21,8 +21,8 @@
 // Contraction split.  A shape with few output tiles (small batch, S and K) would leave most SMs idle while
 // each busy one walks the whole (i, j) range, and a tile count that is not a multiple of the SM count leaves
 // the last wave partly empty.  The launcher can therefore cut the contraction of every tile into nsplit equal
-// slices, one work item each, or (stream) lay the k-blocks of all tiles end to end and give every CTA the
-// same length of that line, whatever tiles it crosses.  All parts of a tile use the same stabilisers (the
+// slices, one work item each, or (stream) run all full waves of tiles whole and share only the tiles of the
+// last, partly filled wave among all CTAs.  All parts of a tile use the same stabilisers (the
 // column maxima are taken over the full I and J), so their accumulators add linearly: in these modes the
 // epilogue adds its raw accumulator into the zero-filled output with red.global.add and
 // lt2exp_finish_kernel then turns the sums into (ma + mb) + log(sum) in place.
@@ -50,8 +50,17 @@ struct Lt2expParams {
   int R, S, I, J, K;
   int tiles_m, tiles_n, num_tiles;
   int nsplit;     // equal slices of the contraction per tile (1: whole tiles)
-  int stream;     // 1: the k-blocks of all tiles form one line that the CTAs share out evenly (see LtWork)
+  int stream;     // 1: whole waves of tiles, then the tiles of the last wave shared among all CTAs (see LtWork)
   int num_items;  // num_tiles * nsplit (not used when stream == 1)
+  int lw_first, lw_parts, lw_main;  // stream == 1: first tile of the last wave and how it is shared (see LtWork)
+  // stream == 1 with scratch memory (both non-null): a tile that several CTAs share is completed without
+  // atomics.  Every part but the first parks its raw partial sums in a slot of `park`
+  // ([slot][MT * BN / 32 chunks][8 column quads][128 rows][4] floats: the 32 lanes of a store write 512
+  // consecutive bytes) and then raises park_flags[slot] (zeroed by the launcher)
+  // by one per epilogue warp; the CTA with the first part adds the parked sums to its own, in slot order, and
+  // writes the finished results.
+  float* park;
+  int* park_flags;
   int vec_ab;            // a and b allow 16-byte loads along k (alignment, strides and K multiples of 4)
   int* status;
   // Chains of layers (all optional, contiguous [R, K]): column maxima of a and of b supplied by the caller
@@ -65,50 +74,108 @@ struct Lt2expParams {
 
 // One work item: the k-blocks [kb_lo, kb_hi) of output tile `tile`.  k-block index = jc * I + i, so a range
 // is whole rows of the (jc, i) grid plus a partial first and last row.
+// park_slot >= 0: the item is not the first part of its tile; with scratch memory its raw sums are parked there.
+// ncollect > 0: the item is the first part of a shared tile and completes it from the slots slot0 .. slot0 + ncollect - 1.
 struct LtItem {
   int tile, kb_lo, kb_hi;
+  int park_slot, slot0, ncollect;
 };
 
 // The work items of one CTA, in the order every role of the CTA walks them.
-//  * stream == 0: item q = tile * nsplit + slice, slices of equal length, items taken round robin over the CTAs;
-//  * stream == 1: the num_tiles * kb_tile k-blocks of the launch form one line, cut into gridDim.x ranges of
-//    equal length (cuts on multiples of 8 k-blocks); a CTA walks its range tile by tile.
+//  * stream == 0: item q = tile * nsplit + slice, slices of equal length, items taken round robin over the CTAs.
+//  * stream == 1 ("whole waves, last wave shared out"): with G CTAs, the first (W - 1) * G tiles run as whole
+//    tiles, round robin, exactly as without any split, so CTAs that read the same rows of w do so at the same
+//    time and the rows cross HBM once.  (Cutting the k-blocks of all tiles into G equal contiguous ranges
+//    balances as well but puts the CTAs that share rows of w at different offsets: measured 45 % slower on
+//    R = 8 and R = 32 entries of 256 x 128 x 128 x 4096 because w then streams from HBM for every column tile.)
+//    The `rem` tiles of the last wave are shared among all G CTAs:
+//      rem <= G / 2:  every tile is cut into P = floor(G / rem) equal parts, part j of tile t on CTA t + j * rem;
+//      rem >  G / 2:  CTA t < rem takes the first `lw_main` k-blocks of tile t, and each of the G - rem other
+//                     CTAs takes the remaining k-blocks ("tails") of tiles u, u + (G - rem), ...; lw_main is
+//                     chosen by the launcher so that a CTA with the most tails is busy as long as a main part.
+//    The first part of a tile completes it (LtItem::ncollect), the other parts are parked or added.
 struct LtWork {
-  int64_t pos, end;
   int q, nq, step;
   int kb_tile, nsplit, stream;
+  int lw_first, lw_rem, lw_parts, lw_main;  // last wave: first tile, tiles, parts per tile (0: mains and tails), main length
+  int phase, tail_next;                     // stream: 0 = whole waves, 1 = last wave, 2 = done
   __device__ LtWork(const Lt2expParams& p, int kb_tile_) {
     kb_tile = kb_tile_;
     nsplit = p.nsplit;
     stream = p.stream;
     q = blockIdx.x;
-    nq = p.num_items;
+    nq = stream ? p.lw_first : p.num_items;
     step = gridDim.x;
-    pos = end = 0;
-    if (stream) {
-      const int64_t total = static_cast<int64_t>(p.num_tiles) * kb_tile;
-      const int64_t g = gridDim.x, c = blockIdx.x;
-      pos = c == 0 ? 0 : ((total * c / g) & ~int64_t(7));
-      end = c == g - 1 ? total : ((total * (c + 1) / g) & ~int64_t(7));
-    }
+    lw_first = p.lw_first;
+    lw_rem = p.num_tiles - p.lw_first;
+    lw_parts = p.lw_parts;
+    lw_main = p.lw_main;
+    phase = 0;
+    tail_next = static_cast<int>(blockIdx.x) - lw_rem;  // (mains and tails) first tail of a helper CTA
   }
   __device__ bool next(LtItem& w) {
-    if (stream) {
-      if (pos >= end) return false;
-      const int64_t tile = pos / kb_tile;
-      w.tile = static_cast<int>(tile);
-      w.kb_lo = static_cast<int>(pos - tile * kb_tile);
-      const int64_t len = end - pos;
-      w.kb_hi = (len < kb_tile - w.kb_lo) ? w.kb_lo + static_cast<int>(len) : kb_tile;
-      pos += w.kb_hi - w.kb_lo;
+    w.park_slot = -1;
+    w.slot0 = 0;
+    w.ncollect = 0;
+    if (!stream) {
+      if (q >= nq) return false;
+      w.tile = q / nsplit;
+      const int sl = q - w.tile * nsplit;
+      w.kb_lo = static_cast<int>(static_cast<int64_t>(sl) * kb_tile / nsplit);
+      w.kb_hi = static_cast<int>(static_cast<int64_t>(sl + 1) * kb_tile / nsplit);
+      q += step;
       return true;
     }
-    if (q >= nq) return false;
-    w.tile = q / nsplit;
-    const int sl = q - w.tile * nsplit;
-    w.kb_lo = static_cast<int>(static_cast<int64_t>(sl) * kb_tile / nsplit);
-    w.kb_hi = static_cast<int>(static_cast<int64_t>(sl + 1) * kb_tile / nsplit);
-    q += step;
+    if (phase == 0) {
+      if (q < nq) {  // whole tiles of the full waves
+        w.tile = q;
+        w.kb_lo = 0;
+        w.kb_hi = kb_tile;
+        q += step;
+        return true;
+      }
+      phase = 1;
+    }
+    if (phase != 1) return false;
+    const int c = blockIdx.x;
+    if (lw_parts > 0) {
+      // equal parts: part j of tile t on CTA t + j * rem
+      phase = 2;
+      const int j = c / lw_rem, t = c - j * lw_rem;
+      if (j >= lw_parts) return false;
+      w.tile = lw_first + t;
+      w.kb_lo = static_cast<int>(static_cast<int64_t>(j) * kb_tile / lw_parts);
+      w.kb_hi = static_cast<int>(static_cast<int64_t>(j + 1) * kb_tile / lw_parts);
+      if (lw_parts > 1) {
+        if (j == 0) {
+          w.slot0 = t * (lw_parts - 1);
+          w.ncollect = lw_parts - 1;
+        } else {
+          w.park_slot = t * (lw_parts - 1) + (j - 1);
+        }
+      }
+      return true;
+    }
+    if (c < lw_rem) {
+      // main part of tile c
+      phase = 2;
+      w.tile = lw_first + c;
+      w.kb_lo = 0;
+      w.kb_hi = lw_main;
+      w.slot0 = c;
+      w.ncollect = lw_main < kb_tile ? 1 : 0;
+      return true;
+    }
+    // tails of tiles u, u + (G - rem), ...
+    if (tail_next >= lw_rem || lw_main >= kb_tile) {
+      phase = 2;
+      return false;
+    }
+    w.tile = lw_first + tail_next;
+    w.kb_lo = lw_main;
+    w.kb_hi = kb_tile;
+    w.park_slot = tail_next;
+    tail_next += static_cast<int>(gridDim.x) - lw_rem;
     return true;
   }
 };
@@ -260,7 +327,8 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
 
   const int JC = (p.J + BK - 1) / BK;  // j-chunks; the k-blocks of a work item are (jc, i), i fastest
   const int KBT = JC * p.I;            // k-blocks per output tile
-  const bool split_mode = p.nsplit > 1 || p.stream != 0;  // partial sums are added into the zero-filled output
+  const bool parking = p.stream != 0 && p.park != nullptr;  // shared tiles are completed through scratch memory
+  const bool split_mode = (p.nsplit > 1 || p.stream != 0) && !parking;  // partial sums are added into the zero-filled output
 
   // Output tile -> (r, n0 = first column, s0 = first row).
   auto decode = [&](int tile, int& r, int& n0, int& s0) {
@@ -361,6 +429,26 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       const int KB = w.kb_hi - w.kb_lo;
       const int nch = Cfg::PROMOTE ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
       const int slot = tcount & 1;
+      // Stream mode with scratch memory: a part that is not the first of its tile parks its sums; the first part
+      // of a shared tile collects them.
+      const bool park_it = parking && w.park_slot >= 0;
+      const bool collect = parking && w.ncollect > 0;
+      if (collect) {
+        // The other parts run at the same time on other CTAs and end about when this one does.
+        for (int cc = 0; ok && cc < w.ncollect; ++cc) {
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(p.park_flags + w.slot0 + cc) < 4) {
+            if (*ctl.flag || clock64() - t0 > WAIT_LIMIT_CYCLES) {
+              raise_abort(ctl, STATUS_TIMEOUT_EPILOGUE);
+              ok = false;
+              break;
+            }
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      constexpr int PARK_TILE = MT * BN * BM;  // floats per parked tile
       for (int ch = 0; ok && ch < nch; ++ch, ++ccount) {
         const int buf = ccount % Cfg::NBUF;
         const uint32_t aph = (ccount / Cfg::NBUF) & 1;
@@ -393,6 +481,35 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
                 tmem_ld_wait();
                 tmem_st_32x32(master, v);
                 continue;
+              }
+            }
+            if (park_it) {
+              // Raw sums of this (row block, column chunk) to the part's slot, four columns of 32 rows per store.
+              tmem_ld_wait();
+              float4* dst = reinterpret_cast<float4*>(p.park + static_cast<int64_t>(w.park_slot) * PARK_TILE +
+                                                      static_cast<int64_t>(t * (BN / 32) + c) * BM * 32) +
+                            q * 32 + lane;
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                dst[g * BM] = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]), __uint_as_float(v[g * 4 + 2]),
+                                     __uint_as_float(v[g * 4 + 3]));
+              continue;
+            }
+            if (collect) {
+              tmem_ld_wait();
+              for (int cc = 0; cc < w.ncollect; ++cc) {
+                const float4* src = reinterpret_cast<const float4*>(
+                                        p.park + static_cast<int64_t>(w.slot0 + cc) * PARK_TILE +
+                                        static_cast<int64_t>(t * (BN / 32) + c) * BM * 32) +
+                                    q * 32 + lane;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  const float4 x = __ldcg(src + g * BM);  // written during this launch: not through the read-only path
+                  v[g * 4 + 0] = __float_as_uint(__uint_as_float(v[g * 4 + 0]) + x.x);
+                  v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) + x.y);
+                  v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) + x.z);
+                  v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) + x.w);
+                }
               }
             }
             if (split_mode) {
@@ -454,6 +571,12 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
         if (lane == 0) {
           mbar_arrive(&acc_empty[buf]);
           if (last) mbar_arrive(&msum_empty[slot]);
+        }
+        if (park_it && last) {
+          // This warp's rows of the partial sums are written: publish them (one count per epilogue warp).
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) add_release_gpu(p.park_flags + w.park_slot, 1);
         }
       }
     }

@@ -144,6 +144,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// ----------------------------------------------------------------------------- flags in global memory
+//
+// Hand-over between CTAs of one launch: the writer makes its data visible (__threadfence) and raises a counter
+// with release semantics; the reader polls the counter with acquire semantics (always with a bound on the
+// number of polls or cycles) and then reads the data with ordinary, not read-only-path, loads.
+__device__ __forceinline__ void add_release_gpu(int* addr, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
 // ----------------------------------------------------------------------------- programmatic dependent launch
 //
 // A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the kernel before
