@@ -76,6 +76,33 @@ def test_tmem_operand_pair_kernel_unaligned_result():
     _assert_close(got, a, b, "tf32")
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("shape", [(40, 300, 100, 520), (64, 512, 75, 256), (33, 260, 1030, 130)])
+def test_pair_kernel_on_batches_of_several_waves(shape, precision):
+    """The CTA-pair kernel on batches of several waves of tiles (the pre-pass and the contraction kernel launched
+    as programmatic dependents): ragged J and K, late entries with all -inf columns, huge column offsets.  The
+    pre-pass maxima are exact, so the result is bit for bit that of a call that is given the column maxima."""
+    import triturus_b200 as tb
+
+    R, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    a = torch.rand(R, I, J, generator=g)
+    b = torch.randn(R, J, K, generator=g) * 8.0 + 150.0 * torch.randn(R, 1, K, generator=g)
+    b[R - 1, :, 5] = float("-inf")
+    b[R // 2, :, K - 1] = float("-inf")
+    b[torch.rand(R, J, K, generator=g) < 0.02] = float("-inf")
+    ad, bd = a.cuda(), b.cuda()
+    got = tb.lm2exp(ad, bd, precision=precision, variant=2564)
+    tb.check_status()
+    assert torch.all(got[R - 1, :, 5] == float("-inf")) and torch.all(got[R // 2, :, K - 1] == float("-inf"))
+    rs = [0, R // 2, R - 1]
+    res = orc.compare_logspace(got[rs].cpu(), orc.lm2exp_fp64(a[rs], b[rs]), ATOL[precision])
+    assert res["ok"], res
+    same = tb.lm2exp(ad, bd, precision=precision, variant=2564, b_colmax=bd.amax(dim=1))
+    tb.check_status()
+    assert torch.equal(got, same)
+
+
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_variants_on_ragged_shape(precision, variant):
