@@ -198,17 +198,23 @@ def test_workload_generators_are_seeded_and_shaped():
 def test_host_pipeline_chunking():
     from triturus_b200.host import chunk_bounds
 
-    assert len(chunk_bounds(32, 12 << 20)) == 12  # 384 MB of input in ~32 MB chunks
-    for batch, chunks in ((7, 3), (5, 16), (1, None), (64, None), (3, 1)):
-        bounds = chunk_bounds(batch, 1 << 20, chunks)
+    def check(bounds, batch):
         assert bounds[0][0] == 0 and bounds[-1][1] == batch
         assert all(lo < hi for lo, hi in bounds)
         assert all(bounds[i][1] == bounds[i + 1][0] for i in range(len(bounds) - 1))
-        sizes = [hi - lo for lo, hi in bounds]
-        assert max(sizes) - min(sizes) <= 1
-        if chunks is not None:
-            assert len(bounds) == min(chunks, batch)
-    assert len(chunk_bounds(1000, 1 << 30)) == 16
-    assert len(chunk_bounds(4, 1 << 10)) == 1
+        return [hi - lo for lo, hi in bounds]
+
+    # explicit chunk counts: equal sizes
+    for batch, chunks in ((7, 3), (5, 16), (3, 1), (64, 9)):
+        sizes = check(chunk_bounds(batch, 1 << 20, chunks), batch)
+        assert max(sizes) - min(sizes) <= 1 and len(sizes) == min(chunks, batch)
+    # automatic: ~32 MB chunks with a short ramp at both ends (cfg2: 32 entries of 8 MB -> 1, 2, 4 ... 4, 2, 1)
+    sizes = check(chunk_bounds(32, 8 << 20), 32)
+    assert sizes[:2] == [1, 2] and sizes[-2:] == [2, 1] and max(sizes) <= 5 and min(sizes[2:-2]) >= 3
+    assert check(chunk_bounds(1, 1 << 30), 1) == [1]
+    assert check(chunk_bounds(4, 1 << 10), 4) == [4]            # small problems: one chunk
+    assert len(check(chunk_bounds(1000, 1 << 30), 1000)) == 16  # huge entries: one per chunk, at most 16 chunks
+    for batch in (2, 3, 9, 64, 129):
+        check(chunk_bounds(batch, 12 << 20), batch)
     with pytest.raises(ValueError):
         chunk_bounds(0, 4)

@@ -311,3 +311,20 @@ def test_transposed_a_with_odd_rows_falls_back_to_a_copy():
     got = tb.lm2exp(a_t.cuda().transpose(1, 2), b.cuda(), precision="3xtf32")
     tb.check_status()
     _assert_close(got.cpu(), a_t.transpose(1, 2).contiguous(), b, "3xtf32")
+
+
+def test_batches_beyond_the_grid_limit():
+    """More than 65535 batch entries (the reference's 1-D grid takes any batch, triturus/lm2exp.py:177-181): the
+    library runs them in blocks of 65535 on the same stream."""
+    import triturus_b200 as tb
+
+    g = torch.Generator().manual_seed(70001)
+    R = 70001
+    a = torch.rand(R, 3, 5, generator=g)
+    b = torch.randn(R, 5, 8, generator=g) * 4.0
+    b[R - 1, :, 2] = float("-inf")
+    for variant in (0, 100000):  # fused max pass; pre-pass through the workspace
+        got = tb.lm2exp(a.cuda(), b.cuda(), precision="3xtf32", variant=variant)
+        tb.check_status()
+        _assert_close(got.cpu(), a, b, "3xtf32")
+    assert torch.equal(tb.colmax(b.cuda()).cpu(), b.amax(dim=1).clamp(-1e38, 1e38))

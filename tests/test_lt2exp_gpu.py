@@ -398,3 +398,16 @@ def test_contraction_split_odd_columns(precision, variant):
     want = orc.lt2exp_fp64(w, a, b)
     assert torch.all(got[0, :, 140] == float("-inf"))
     _assert_close(got, w, a, b, precision, want)
+
+
+def test_batches_beyond_the_grid_limit():
+    """More than 65535 batch entries run in blocks of 65535 on the same stream (whole tiles and split contraction)."""
+    g = torch.Generator().manual_seed(66000)
+    R = 66000
+    w = torch.rand(R, 2, 3, 4, generator=g)
+    a = torch.randn(R, 3, 8, generator=g) * 3.0
+    b = torch.randn(R, 4, 8, generator=g) * 3.0
+    a[R - 1, :, 1] = float("-inf")
+    for variant in (10000, 2 * 10000):
+        got = _run(w, a, b, precision="3xtf32", variant=variant)
+        _assert_close(got, w, a, b, "3xtf32")

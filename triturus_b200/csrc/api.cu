@@ -442,7 +442,15 @@ int triturus_b200_selftest_wait_timeout(int32_t* status_dev, int64_t limit_cycle
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
                              void* stream) {
   if (x == nullptr || m == nullptr || x_strides == nullptr) return TRITURUS_B200_EINVAL;
-  if (R <= 0 || J <= 0 || K <= 0 || R > 65535 || J > INT32_MAX || K > INT32_MAX) return TRITURUS_B200_EINVAL;
+  if (R <= 0 || J <= 0 || K <= 0 || J > INT32_MAX || K > INT32_MAX) return TRITURUS_B200_EINVAL;
+  if (R > 65535) {  // gridDim.y holds the batch: block by block beyond its limit
+    for (int64_t r0 = 0; r0 < R; r0 += 65535) {
+      const int rc = triturus_b200_colmax_f32(x + r0 * x_strides[0], m + r0 * K, R - r0 < 65535 ? R - r0 : 65535, J,
+                                              K, x_strides, stream);
+      if (rc != TRITURUS_B200_OK) return rc;
+    }
+    return TRITURUS_B200_OK;
+  }
   if (K > 1 && x_strides[2] != 1) return TRITURUS_B200_EALIGN;
   const bool vec = (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
   const dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(R));
@@ -486,7 +494,7 @@ size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int
 
 // Shared body of the lm2exp entry points.  b_colmax (optional): [R, K] column maxima of b supplied by the
 // caller, which replace the stabiliser pass.  out_colmax (optional): [R, K] receives max_i out[r, i, k].
-static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
                       const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
                       int precision, int variant, const float* b_colmax, float* out_colmax, void* workspace,
                       size_t workspace_bytes, int32_t* status_dev, void* stream) {
@@ -628,6 +636,30 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
   if (plan.promote_tf32)
     return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmP_128_1>(ta, tb, to, p, st, dep);
   return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st, dep);
+}
+
+// Batches of more than 65535 entries (the limit of gridDim.y / .z in the small kernels) run block by block on
+// the same stream; the reference's 1-D grid takes any batch (triturus/lm2exp.py:177-181).
+constexpr int64_t kMaxBatchBlock = 65535;
+
+static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
+                      const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
+                      int precision, int variant, const float* b_colmax, float* out_colmax, void* workspace,
+                      size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  if (R <= kMaxBatchBlock || a == nullptr || b == nullptr || out == nullptr || a_strides == nullptr ||
+      b_strides == nullptr || out_strides == nullptr)
+    return lm2exp_run_block(a, b, out, R, I, J, K, a_strides, b_strides, out_strides, precision, variant, b_colmax,
+                            out_colmax, workspace, workspace_bytes, status_dev, stream);
+  for (int64_t r0 = 0; r0 < R; r0 += kMaxBatchBlock) {
+    const int64_t n = std::min(kMaxBatchBlock, R - r0);
+    const int rc = lm2exp_run_block(a + r0 * a_strides[0], b + r0 * b_strides[0], out + r0 * out_strides[0], n, I, J,
+                                    K, a_strides, b_strides, out_strides, precision, variant,
+                                    b_colmax != nullptr ? b_colmax + r0 * K : nullptr,
+                                    out_colmax != nullptr ? out_colmax + r0 * K : nullptr, workspace, workspace_bytes,
+                                    status_dev, stream);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  return TRITURUS_B200_OK;
 }
 
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
@@ -882,7 +914,7 @@ static int lt2exp_variant(int variant, int precision, int64_t R, int64_t S, int6
 
 static int lt2exp_check_dims(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision) {
   if (R <= 0 || S <= 0 || I <= 0 || J <= 0 || K <= 0) return TRITURUS_B200_EINVAL;
-  if (R > 65535 || S > (1 << 30) || I > (1 << 24) || J > (1 << 24) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
+  if (R > INT32_MAX || S > (1 << 30) || I > (1 << 24) || J > (1 << 24) || K > (1 << 30)) return TRITURUS_B200_EINVAL;
   if (((J + 31) / 32) * I > (1 << 28)) return TRITURUS_B200_EINVAL;
   if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
     return TRITURUS_B200_EINVAL;
@@ -957,7 +989,7 @@ extern "C" size_t triturus_b200_lt2exp_workspace_bytes(int64_t R, int64_t S, int
 // Shared body of the lt2exp entry points.  a_colmax / b_colmax (optional, both or neither): [R, K] column
 // maxima of a and b, which replace the scan at the start of every tile.  out_colmax (optional): [R, K] receives
 // max_s out[r, s, k].
-static int lt2exp_run(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S, int64_t I,
+static int lt2exp_run_block(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S, int64_t I,
                       int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
                       const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
                       const float* a_colmax, const float* b_colmax, float* out_colmax, void* workspace,
@@ -1032,6 +1064,28 @@ static int lt2exp_run(const float* w, const float* a, const float* b, float* out
 
   const tb200::LtLaunch L{split, static_cast<cudaStream_t>(stream), nullptr, workspace, workspace_bytes};
   return lt2exp_dispatch(precision, bn, mt, promote, tw, p, L);
+}
+
+static int lt2exp_run(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S, int64_t I,
+                      int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],
+                      const int64_t b_strides[3], const int64_t out_strides[3], int precision, int variant,
+                      const float* a_colmax, const float* b_colmax, float* out_colmax, void* workspace,
+                      size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  if (R <= kMaxBatchBlock || w == nullptr || a == nullptr || b == nullptr || out == nullptr ||
+      w_strides == nullptr || a_strides == nullptr || b_strides == nullptr || out_strides == nullptr)
+    return lt2exp_run_block(w, a, b, out, R, S, I, J, K, w_strides, a_strides, b_strides, out_strides, precision,
+                            variant, a_colmax, b_colmax, out_colmax, workspace, workspace_bytes, status_dev, stream);
+  for (int64_t r0 = 0; r0 < R; r0 += kMaxBatchBlock) {
+    const int64_t n = std::min(kMaxBatchBlock, R - r0);
+    const int rc = lt2exp_run_block(w + r0 * w_strides[0], a + r0 * a_strides[0], b + r0 * b_strides[0],
+                                    out + r0 * out_strides[0], n, S, I, J, K, w_strides, a_strides, b_strides,
+                                    out_strides, precision, variant, a_colmax != nullptr ? a_colmax + r0 * K : nullptr,
+                                    b_colmax != nullptr ? b_colmax + r0 * K : nullptr,
+                                    out_colmax != nullptr ? out_colmax + r0 * K : nullptr, workspace, workspace_bytes,
+                                    status_dev, stream);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  return TRITURUS_B200_OK;
 }
 
 extern "C" int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R,

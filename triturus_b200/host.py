@@ -35,20 +35,35 @@ def _streams(dev: torch.device):
 
 
 def chunk_bounds(batch: int, bytes_per_entry: int, chunks: int | None = None) -> list[tuple[int, int]]:
-    """Cut `batch` entries into contiguous chunks: `chunks` of them if given, else as many as keep each
-    chunk at about 32 MB of input (at least 1, at most 16 and at most `batch`)."""
+    """Cut `batch` entries into contiguous chunks.
+
+    `chunks` given: that many chunks of equal size (at most `batch`).  Otherwise chunks of about 32 MB of input
+    with shorter ones at both ends (a quarter, then half of that size): the first copy-in and the last copy-out
+    are the only transfers that nothing overlaps, so they are kept short, while the chunks in between are long
+    enough to run at the full PCIe / C2C rate."""
     if batch <= 0:
         raise ValueError("empty batch")
-    if chunks is None:
-        total = batch * max(bytes_per_entry, 1)
-        chunks = max(1, min(16, total // _TARGET_CHUNK_BYTES))
-    chunks = max(1, min(int(chunks), batch))
-    base, extra = divmod(batch, chunks)
+    if chunks is not None:
+        chunks = max(1, min(int(chunks), batch))
+        base, extra = divmod(batch, chunks)
+        sizes = [base + (1 if c < extra else 0) for c in range(chunks)]
+    else:
+        per = max(bytes_per_entry, 1)
+        if batch * per < 2 * _TARGET_CHUNK_BYTES:
+            sizes = [batch]
+        else:
+            full = max(1, _TARGET_CHUNK_BYTES // per)
+            ramp = [s for s in (max(1, full // 4), max(1, full // 2)) if s < full]
+            if 2 * sum(ramp) + full > batch:
+                ramp = []
+            middle = batch - 2 * sum(ramp)
+            n_mid = max(1, min(16, -(-middle // full)))
+            base, extra = divmod(middle, n_mid)
+            sizes = ramp + [base + (1 if c < extra else 0) for c in range(n_mid)] + ramp[::-1]
     bounds, lo = [], 0
-    for c in range(chunks):
-        hi = lo + base + (1 if c < extra else 0)
-        bounds.append((lo, hi))
-        lo = hi
+    for size in sizes:
+        bounds.append((lo, lo + size))
+        lo += size
     return bounds
 
 
