@@ -182,6 +182,18 @@ int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int
                              void* stream);
 
 /*
+ * Plain matrix product out[M,N] = a[M,K] * b[K,N] through the same pipeline with the log-space steps switched off.
+ * Replaces triturus/mm.py:181-214 (wrapper) and :91-178 (_ker_mm).  precision TF32: both operands rounded to the
+ * nearest tf32, as the reference's kernel does with cvt.rna (triturus/mm.py:152-154, triturus/utils.py:56-63);
+ * precision 3XTF32: the hi/lo split, ~fp32 accuracy (the reference's "ieee" dot).  Strides in elements, innermost
+ * stride 1, row strides multiples of 4 elements, bases 16-byte aligned.  No workspace.  Inf / NaN inputs are not
+ * supported in TF32 mode (the rounding is done on the bit pattern).
+ */
+int triturus_b200_mm_f32(const float* a, const float* b, float* out, int64_t M, int64_t K, int64_t N,
+                         const int64_t a_strides[2], const int64_t b_strides[2], const int64_t out_strides[2],
+                         int precision, int32_t* status_dev, void* stream);
+
+/*
  * Self-test of the error path behind `status_dev` (no counterpart in the reference, whose kernels have no waits
  * that could time out apart from the unbounded spin lock of triturus/lt2exp.py:498-506).  Launches one 64-thread
  * block in which a warp waits on a barrier that nobody signals, with a wait limit of `limit_cycles` GPU clock

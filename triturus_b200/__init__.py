@@ -10,6 +10,7 @@ from ._native import NativeLibraryError, check_status, colmax
 from .host import lm2exp_host, lt2exp_host
 from .lm2exp import lm2exp
 from .lt2exp import lt2exp
+from .mm import mm
 from .utils import (
     ensure_reproducibility,
     is_torch_tf32_enabled,
@@ -28,5 +29,6 @@ __all__ = [
     "lm2exp_host",
     "lt2exp",
     "lt2exp_host",
+    "mm",
     "set_tf32_enabled",
 ]

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "triturus_b200_lt2exp_chain_f32",
     "triturus_b200_colmax_f32",
     "triturus_b200_selftest_wait_timeout",
+    "triturus_b200_mm_f32",
     "triturus_b200_lm2exp_static_max_columns",
     "triturus_b200_lm2exp_f32_static",
 )
@@ -130,6 +131,9 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     ]  # fmt: skip
     lib.triturus_b200_selftest_wait_timeout.restype = c_int
     lib.triturus_b200_selftest_wait_timeout.argtypes = [c_void_p, c_int64, c_void_p]
+    lib.triturus_b200_mm_f32.restype = c_int
+    lib.triturus_b200_mm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, i64p, i64p, i64p,
+                                         c_int, c_void_p, c_void_p]  # fmt: skip
     lib.triturus_b200_colmax_f32.restype = c_int
     lib.triturus_b200_colmax_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, i64p, c_void_p]
     return lib
@@ -348,6 +352,24 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
             _status_word(a.device).data_ptr(), _raw_stream(idx),
         )  # fmt: skip
     _check(rc, "triturus_b200_lt2exp_ws_f32")
+    return out
+
+
+def mm_impl(a: torch.Tensor, b: torch.Tensor, precision: int) -> torch.Tensor:
+    """out = a @ b for 2-D fp32 CUDA tensors through the contraction pipeline (the reference's triturus/mm.py)."""
+    _require_cuda(a, b)
+    a = _tma_ready(a)
+    b = _tma_ready(b)
+    M, K = a.shape
+    N = b.shape[1]
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    with _on_device(a.device) as idx:
+        rc = LIB.triturus_b200_mm_f32(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, K, N,
+            (c_int64 * 2)(*a.stride()), (c_int64 * 2)(*b.stride()), (c_int64 * 2)(*out.stride()),
+            int(precision), _status_word(a.device).data_ptr(), _raw_stream(idx),
+        )  # fmt: skip
+    _check(rc, "triturus_b200_mm_f32")
     return out
 
 

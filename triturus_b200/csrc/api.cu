@@ -230,6 +230,10 @@ using LmX_128_2 = Lm2expCfg<128, 2, 1, 2>;
 using LmP_128_1 = Lm2expCfg<128, 1, 0, 6, true>;
 using LmP_128_2 = Lm2expCfg<128, 2, 0, 4, true>;
 
+// plain matrix product (the reference's mm): 256 x 128 tiles, no stabiliser / exp / log
+using LmPlainT = Lm2expCfg<128, 2, 0, 4, false, true>;
+using LmPlainX = Lm2expCfg<128, 2, 1, 2, true, true>;
+
 using LmPairT = Lm2expPairCfg<0, 6>;
 using LmPairX = Lm2expPairCfg<1, 3>;
 
@@ -660,6 +664,67 @@ static int lm2exp_run(const float* a, const float* b, float* out, int64_t R, int
     if (rc != TRITURUS_B200_OK) return rc;
   }
   return TRITURUS_B200_OK;
+}
+
+int triturus_b200_mm_f32(const float* a, const float* b, float* out, int64_t M, int64_t K, int64_t N,
+                         const int64_t a_strides[2], const int64_t b_strides[2], const int64_t out_strides[2],
+                         int precision, int32_t* status_dev, void* stream) {
+  if (a == nullptr || b == nullptr || out == nullptr || a_strides == nullptr || b_strides == nullptr ||
+      out_strides == nullptr)
+    return TRITURUS_B200_EINVAL;
+  if (M <= 0 || K <= 0 || N <= 0 || M > (1 << 30) || K > (1 << 30) || N > (1 << 30)) return TRITURUS_B200_EINVAL;
+  if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
+    return TRITURUS_B200_EINVAL;
+  // out[i, k] = sum_j a[i, j] * b[j, k]: the lm2exp pipeline on one batch entry with the transform switched off
+  int64_t as0 = a_strides[0], bs0 = b_strides[0], os0 = out_strides[0];
+  if ((K > 1 && a_strides[1] != 1) || (N > 1 && (b_strides[1] != 1 || out_strides[1] != 1))) return TRITURUS_B200_EALIGN;
+  if (!aligned16(a) || !aligned16(b)) return TRITURUS_B200_EALIGN;
+  if (!fix_stride(M, as0, round_up4(K)) || !fix_stride(K, bs0, round_up4(N))) return TRITURUS_B200_EALIGN;
+  if (M > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
+  CUtensorMap ta, tb, to;
+  memset(&to, 0, sizeof(to));
+  int rc;
+  {
+    const int64_t dims[3] = {K, M, 1};
+    const int64_t strides[3] = {1, as0, as0 * M};
+    const uint32_t box[3] = {32, 128, 1};
+    rc = make_tmap(&ta, a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  {
+    const int64_t dims[3] = {N, K, 1};
+    const int64_t strides[3] = {1, bs0, bs0 * K};
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tmap(&tb, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  int64_t tos0 = os0;
+  const bool out_tma = aligned16(out) && (N & 3) == 0 && fix_stride(M, tos0, round_up4(N));
+  if (out_tma) {
+    const int64_t dims[3] = {N, M, 1};
+    const int64_t strides[3] = {1, tos0, tos0 * M};
+    const uint32_t box[3] = {32, 32, 1};
+    rc = make_tmap(&to, out, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  }
+  Lm2expParams p;
+  p.out_tma = out_tma ? 1 : 0;
+  p.a_mn = 0;
+  p.m_ws = nullptr;
+  p.out = out;
+  p.out_max = nullptr;
+  p.out_s0 = os0 * M;
+  p.out_s1 = os0;
+  p.R = 1;
+  p.I = static_cast<int>(M);
+  p.J = static_cast<int>(K);
+  p.K = static_cast<int>(N);
+  p.tiles_m = p.tiles_n = p.num_tiles = 0;
+  p.fused_max = 0;
+  p.status = status_dev;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp<LmPlainX>(ta, tb, to, p, st, false)
+                                                      : launch_lm2exp<LmPlainT>(ta, tb, to, p, st, false);
 }
 
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,

@@ -47,10 +47,14 @@ struct Lm2expParams {
   int* status;
 };
 
-template <int BN_, int MT_, int PREC_, int NS_, bool PROMOTE_ = (PREC_ != 0)>
+// PLAIN_ = true turns the kernel into a plain batched matrix product out = a * b (the reference's `mm`,
+// triturus/mm.py:181-214): no stabiliser, no exp, no log; in the single-pass TF32 mode both operands are rounded
+// to nearest tf32 as the reference's kernel does with cvt.rna (triturus/mm.py:152-154, triturus/utils.py:56-63).
+template <int BN_, int MT_, int PREC_, int NS_, bool PROMOTE_ = (PREC_ != 0), bool PLAIN_ = false>
 struct Lm2expCfg {
   static constexpr int BM = 128, BK = 32, NTW = 8;
   static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_;
+  static constexpr bool PLAIN = PLAIN_;
   static constexpr int NCOPY = PREC ? 2 : 1;               // hi (+ lo) copies of each operand
   static constexpr int A_TILE = BM * BK * 4;               // 16 KB
   static constexpr int B_BOX = 32 * BK * 4;                // one 32-column group: 4 KB
@@ -377,10 +381,17 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               const float4 m4 = m4p[g];  // same address in every lane: broadcast
               const float a0 = __uint_as_float(v[h][g * 4 + 0]), a1 = __uint_as_float(v[h][g * 4 + 1]);
               const float a2 = __uint_as_float(v[h][g * 4 + 2]), a3 = __uint_as_float(v[h][g * 4 + 3]);
-              o[g * 4 + 0] = m4.x + (PREC ? logf(a0) : lg2_approx(a0) * LN2_F);
-              o[g * 4 + 1] = m4.y + (PREC ? logf(a1) : lg2_approx(a1) * LN2_F);
-              o[g * 4 + 2] = m4.z + (PREC ? logf(a2) : lg2_approx(a2) * LN2_F);
-              o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
+              if (Cfg::PLAIN) {
+                o[g * 4 + 0] = a0;
+                o[g * 4 + 1] = a1;
+                o[g * 4 + 2] = a2;
+                o[g * 4 + 3] = a3;
+              } else {
+                o[g * 4 + 0] = m4.x + (PREC ? logf(a0) : lg2_approx(a0) * LN2_F);
+                o[g * 4 + 1] = m4.y + (PREC ? logf(a1) : lg2_approx(a1) * LN2_F);
+                o[g * 4 + 2] = m4.z + (PREC ? logf(a2) : lg2_approx(a2) * LN2_F);
+                o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
+              }
             }
             // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
             // (16-byte chunk g at position g ^ (row % 8): conflict-free).
@@ -535,6 +546,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         ++max_passes;
 #pragma unroll
         for (int x = 0; x < 4; ++x) m4[x] = clamp_stab(mx[x]);
+      } else if (Cfg::PLAIN) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) m4[x] = 0.f;  // plain product: no stabiliser
       } else {
         const float* mrow = p.m_ws + static_cast<int64_t>(r) * p.K;
 #pragma unroll
@@ -580,10 +594,18 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           // run unconditionally and interleave; a branch around each one would serialise them.
           const bool rowv = j < jrem;
           float e[4];
-          e[0] = exp_shifted((rowv && colv[0]) ? v[x].x : -INFINITY, m4[0]);
-          e[1] = exp_shifted((rowv && colv[1]) ? v[x].y : -INFINITY, m4[1]);
-          e[2] = exp_shifted((rowv && colv[2]) ? v[x].z : -INFINITY, m4[2]);
-          e[3] = exp_shifted((rowv && colv[3]) ? v[x].w : -INFINITY, m4[3]);
+          if (Cfg::PLAIN) {
+            // plain product: b itself is the operand (zeros in the padding)
+            e[0] = (rowv && colv[0]) ? v[x].x : 0.f;
+            e[1] = (rowv && colv[1]) ? v[x].y : 0.f;
+            e[2] = (rowv && colv[2]) ? v[x].z : 0.f;
+            e[3] = (rowv && colv[3]) ? v[x].w : 0.f;
+          } else {
+            e[0] = exp_shifted((rowv && colv[0]) ? v[x].x : -INFINITY, m4[0]);
+            e[1] = exp_shifted((rowv && colv[1]) ? v[x].y : -INFINITY, m4[1]);
+            e[2] = exp_shifted((rowv && colv[2]) ? v[x].z : -INFINITY, m4[2]);
+            e[3] = exp_shifted((rowv && colv[3]) ? v[x].w : -INFINITY, m4[3]);
+          }
           if (PREC) {
             float4 h;
             tf32_split_rn(e[0], h.x, lo[x].x);
@@ -616,6 +638,17 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             tf32_split_trunc(v.w, h.w, l.w);
             ah[ch] = h;
             al[ch] = l;
+          }
+        } else if (Cfg::PLAIN) {
+          // Plain single-pass TF32 product: round a to the nearest tf32 as well (the tensor core would truncate).
+          uint4* ah = reinterpret_cast<uint4*>(a_tile(s, 0, 0));
+          for (int ch = tt; ch < MT * Cfg::A_TILE / 16; ch += Cfg::NTT) {
+            uint4 v = ah[ch];
+            v.x += 0x1000u;
+            v.y += 0x1000u;
+            v.z += 0x1000u;
+            v.w += 0x1000u;
+            ah[ch] = v;
           }
         }
         fence_proxy_async_smem();
