@@ -52,16 +52,32 @@ const char* triturus_b200_strerror(int code);
  *   precision: TRITURUS_B200_PRECISION_*.
  *   variant:   0 = choose everything from the problem size; otherwise STAB * 100000 + BN * 10 + MT with
  *              BN in {128, 256} output columns and MT in {1, 2} 128-row blocks per CTA tile (BN * 10 + MT
- *              may be 0 = automatic; 2564 = a 256 x 256 tile computed by a pair of CTAs, 128 rows each)
+ *              may be 0 = automatic; 2564 = a 256 x 256 tile computed by a pair of CTAs, 128 rows each;
+ *              2566 = the same tile with the generated operand exp(b - m) kept in tensor memory, plain TF32
+ *              only; 2567 = 2566 with the optimistic stabiliser described below)
  *              and STAB selecting where the stabiliser is computed: 0 = automatic, 1 = pre-pass launch
- *              writing the workspace, 2 = max pass fused into the contraction kernel (not with 2564).
+ *              writing the workspace, 2 = max pass fused into the contraction kernel (not with the pair tiles).
  *              (The counterpart of the reference's autotune table, triturus/lm2exp.py:7-58.)
- *   workspace: at least triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned; holds the
- *              [R,K] stabiliser.
+ *   workspace: triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned: two flag words padded
+ *              to 256 bytes, then the [R,K] stabiliser.  A workspace of only R * K floats is accepted too; the
+ *              optimistic stabiliser is then not used.  Keep the workspace between calls (or zero its first
+ *              8 bytes once): flag words that are up by accident cost a call the exact passes.
+ *
+ * Optimistic stabiliser (variant 2567; chosen automatically for plain TF32 on pair tiles when a has j
+ * contiguous): no pre-pass over b.  The contraction kernel takes as stabiliser of a column the maximum over its
+ * first 32 rows j; later values may exceed it, exp(b - m) is then larger than 1, which fp32 holds up to e^88.
+ * Only the stabiliser differs from the exact form, so results agree with it to rounding.  A result that
+ * overflowed all the same (+inf or NaN) raises the flag word, and the exact pre-pass and contraction, which
+ * follow in the stream as launches that return at once while the flag is down, redo the whole call and put
+ * the flag down again (a flag word that is up by accident in fresh memory costs one exact pass).  Inputs
+ * whose columns grow by more than ~80 after their first 32 rows therefore cost a second pass.  The reference
+ * finds the exact maximum in a first loop over j inside its kernel (triturus/lm2exp.py:124-127).
  */
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K);
 /* Number of kernels one triturus_b200_lm2exp_f32 call launches for these arguments on the current device:
- * 2 (stabiliser pre-pass + contraction) or 1 (fused max pass); negative on invalid arguments.  The reference
+ * 2 (stabiliser pre-pass + contraction), 1 (fused max pass) or 3 (optimistic stabiliser: the contraction and the
+ * two conditional launches of the exact passes; a with j contiguous and a full-size workspace assumed);
+ * negative on invalid arguments.  The reference
  * has no counterpart (its launch count is Triton's business, triturus/lm2exp.py:186-205). */
 int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,

@@ -40,7 +40,9 @@ def test_version_and_strerror():
 
 def test_workspace_bytes():
     f = _native.LIB.triturus_b200_lm2exp_workspace_bytes
-    assert f(32, 1024, 1024, 1024) == 32 * 1024 * 4
+    # 256 bytes for the flag words of the optimistic stabiliser, then R x K stabilisers
+    assert f(32, 1024, 1024, 1024) == 256 + 32 * 1024 * 4
+    assert f(3, 7, 5, 11) == 256 + 3 * 11 * 4
     assert f(0, 1, 1, 1) == 0
 
 

@@ -67,6 +67,85 @@ def test_tmem_operand_pair_kernel(shape):
         tb.lm2exp(a.cuda(), b.cuda(), precision="3xtf32", variant=2566)
 
 
+def _optimistic_cases():
+    """(name, a, b, takes_the_exact_passes) for the optimistic stabiliser: columns whose later rows stay below,
+    exceed moderately, or overflow past the maximum of their first 32 rows."""
+    g = torch.Generator().manual_seed(2567)
+    rnd = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    uni = lambda *s: torch.rand(*s, generator=g)  # noqa: E731
+    b = rnd(3, 250, 520) * 6.0 + 50.0 * rnd(3, 1, 520)
+    b[0, :, 3] = float("-inf")
+    b[uni(3, 250, 520) < 0.01] = float("-inf")
+    yield "random", uni(3, 300, 250), b, False
+    b = rnd(2, 256, 512)
+    b[:, 100:] += 30.0
+    yield "later-rows-30-above", uni(2, 512, 256), b, False
+    b = rnd(2, 256, 512)
+    b[:, 64:] += 70.0
+    yield "later-rows-70-above", uni(2, 512, 256) * 1e-3, b, False
+    b = torch.arange(1024, dtype=torch.float32).view(1, 1024, 1).expand(2, 1024, 512).contiguous() + rnd(2, 1024, 512)
+    yield "ramp-of-1000", uni(2, 512, 1024), b, True
+    b = rnd(2, 256, 512)
+    b[:, :32] = float("-inf")
+    yield "first-rows-all-neg-inf", uni(2, 512, 256), b, True
+    b = rnd(1, 256, 512)
+    b[0, 200, 77] = 500.0
+    yield "one-spike", uni(1, 512, 256), b, True
+    b = rnd(2, 40, 300)
+    yield "short-contraction", uni(2, 512, 40), b, False
+    b = rnd(40, 8, 512)
+    b[:, 5] += 200.0
+    yield "one-k-block-per-tile", uni(40, 512, 8), b, False
+
+
+@pytest.mark.parametrize("case", list(_optimistic_cases()), ids=lambda c: c[0])
+def test_optimistic_stabiliser(case):
+    """Variant 2567: no pre-pass; the stabiliser of a column is the maximum of its first 32 rows, and a result that
+    overflowed makes the conditional exact passes redo the call.  Either way the result is within the TF32
+    tolerance of float64; where the exact passes ran it is bit for bit the result of the pre-pass variant."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    name, a, b, exact = case
+    R, I, J = a.shape
+    K = b.shape[2]
+    assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, 0, 2567) == 2567
+    assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, 0, 102567) == 102566
+    assert _native.LIB.triturus_b200_lm2exp_launches(R, I, J, K, 0, 2567) == 3
+    ad, bd = a.cuda(), b.cuda()
+    got = tb.lm2exp(ad, bd, precision="tf32", variant=2567)
+    tb.check_status()
+    _assert_close(got.cpu(), a, b, "tf32")
+    pre = tb.lm2exp(ad, bd, precision="tf32", variant=102566)
+    tb.check_status()
+    assert torch.equal(torch.isinf(got), torch.isinf(pre))
+    if exact:
+        assert torch.equal(got, pre)
+    elif name in ("random", "later-rows-30-above", "later-rows-70-above"):
+        # the optimistic result was kept (another stabiliser, so other roundings): the exact passes did not run
+        assert not torch.equal(got, pre)
+    # a clean call afterwards starts from a cleared flag
+    b2 = torch.randn(R, J, K, generator=torch.Generator().manual_seed(1))
+    got2 = tb.lm2exp(ad, b2.cuda(), precision="tf32", variant=2567)
+    tb.check_status()
+    _assert_close(got2.cpu(), a, b2, "tf32")
+    with pytest.raises(tb.NativeLibraryError):
+        tb.lm2exp(ad, bd, precision="3xtf32", variant=2567)
+
+
+def test_optimistic_stabiliser_is_the_automatic_choice_for_tf32_pairs():
+    """cfg2's shape: plain TF32 runs the optimistic TMEM-operand kernel, 3xTF32 the shared-memory pair kernel with
+    the pre-pass; a supplied stabiliser or a forced pre-pass leaves the optimistic form out."""
+    from triturus_b200 import _native
+
+    L = _native.LIB
+    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 0, 0) == 2567
+    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 1, 0) == 102564
+    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 0, 100000) == 102566
+    assert L.triturus_b200_lm2exp_launches(32, 1024, 1024, 1024, 0, 0) == 3
+    assert L.triturus_b200_lm2exp_chain_launches(32, 1024, 1024, 1024, 0, 0, 1, 0) == 1
+
+
 def test_tmem_operand_pair_kernel_unaligned_result():
     """K not a multiple of 4: the wrapper pads b, the result rows are not 16-byte aligned and are written row by row."""
     g = torch.Generator().manual_seed(99)

@@ -182,6 +182,24 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return st
 
 
+_LM_WORKSPACE: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _lm2exp_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """The lm2exp workspace of the current stream of `device`: kept between calls and created zero-filled, so
+    that the flag words at its start (the optimistic stabiliser's) are down unless a call on this stream left
+    them up - a fresh allocation per call would put them on whatever the block held before.  Grows by doubling;
+    calls on one stream are ordered, calls on different streams get different buffers."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, int(_raw_stream(idx)))
+    ws = _LM_WORKSPACE.get(key)
+    if ws is None or ws.numel() * 4 < nbytes:
+        n = max(nbytes, 1 << 16, 0 if ws is None else 2 * ws.numel() * 4)
+        ws = torch.zeros((n + 3) // 4, dtype=torch.float32, device=torch.device("cuda", idx))
+        _LM_WORKSPACE[key] = ws
+    return ws
+
+
 def check_status(device=None) -> None:
     """Synchronise `device` and raise if any kernel launched through this module reported a time-out."""
     if device is None:
@@ -286,8 +304,8 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     b = _tma_ready(b)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
-    ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=a.device)
     with _on_device(a.device) as idx:
+        ws = _lm2exp_workspace(a.device, ws_bytes)
         rc = LIB.triturus_b200_lm2exp_f32(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K,
             _i64(a.stride()), _i64(b.stride()), _i64(out.stride()),
@@ -318,7 +336,8 @@ def _lm2exp_chain_impl(
         ws_ptr, ws_bytes, ws = None, 0, None
     else:
         ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
-        ws = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=a.device)
+        with _on_device(a.device):
+            ws = _lm2exp_workspace(a.device, ws_bytes)
         ws_ptr = ws.data_ptr()
     with _on_device(a.device) as idx:
         rc = LIB.triturus_b200_lm2exp_chain_f32(

@@ -25,11 +25,21 @@ namespace tb200 {
 // folds the four row slots with warp shuffles.
 template <bool VEC>
 __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
-                                                      int64_t s0, int64_t s1) {
+                                                      int64_t s0, int64_t s1, const int* only_if, int* publish) {
   __shared__ float part[8][32];
   // The contraction kernel that consumes m may be launched as a programmatic dependent: let it start its set-up
   // (barriers, tensor memory, first operand tiles) as soon as every block of this grid is running.
   pdl_launch_dependents();
+  // A conditional launch (the exact pass behind an optimistic contraction, launched as that kernel's programmatic
+  // dependent) waits for it and does nothing unless it raised the flag.
+  // Block 0 republishes the decision in a second word for the conditional contraction behind this launch, so
+  // that that kernel can put the flag itself down again without a reader still being out.
+  if (only_if != nullptr) {
+    pdl_wait();
+    const bool up = *only_if != 0;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *publish = up ? 1 : 0;
+    if (!up) return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.y;
   const int c0 = blockIdx.x * 32;
@@ -181,10 +191,10 @@ static int64_t round_up4(int64_t v) { return (v + 3) & ~int64_t(3); }
 // `after_prepass`: the stabiliser pre-pass was launched just before on the same stream; the kernel is then
 // launched as its programmatic dependent (its threads wait for the pre-pass before they read m).
 template <class Kern, class... Args>
-static int launch_maybe_dependent(Kern kern, int grid, int threads, int smem, cudaStream_t stream, bool after_prepass,
+static int launch_maybe_dependent(Kern kern, dim3 grid, int threads, int smem, cudaStream_t stream, bool after_prepass,
                                   Args... args) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.gridDim = grid;
   cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem);
   cfg.stream = stream;
@@ -215,7 +225,8 @@ static int launch_lm2exp(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  return launch_maybe_dependent(kern, grid, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb, to, p);
+  return launch_maybe_dependent(kern, dim3(static_cast<unsigned>(grid)), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta,
+                                tb, to, p);
 }
 
 //                          BN   MT PREC NS
@@ -274,16 +285,18 @@ static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, cons
   if (nt > INT32_MAX) return TRITURUS_B200_EINVAL;
   p.num_tiles = static_cast<int>(nt);
   const int clusters = p.num_tiles < max_clusters[dev] ? p.num_tiles : max_clusters[dev];
-  return launch_maybe_dependent(kern, 2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb, to,
-                                p);
+  return launch_maybe_dependent(kern, dim3(static_cast<unsigned>(2 * clusters)), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream,
+                                after_prepass, ta, tb, to, p);
 }
 
-using LmTsPair = Lm2expTsPairCfg<8, 4>;
+//                                  NS NSB groups optimistic
+using LmTsPair = Lm2expTsPairCfg<8, 4, 2>;
+using LmTsPairOpt = Lm2expTsPairCfg<8, 4, 2, true>;
 
 // The CTA-pair kernel with the generated operand in tensor memory (plain TF32, a with j contiguous).
+template <class Cfg>
 static int launch_lm2exp_tspair(const CUtensorMap& ta, const CUtensorMap& tb_plain, const CUtensorMap& to,
                                 Lm2expParams p, cudaStream_t stream, bool after_prepass) {
-  using Cfg = LmTsPair;
   auto kern = lm2exp_tspair_kernel<Cfg>;
   static std::once_flag once[64];
   static cudaError_t attr_rc[64];
@@ -301,8 +314,8 @@ static int launch_lm2exp_tspair(const CUtensorMap& ta, const CUtensorMap& tb_pla
   p.num_tiles = static_cast<int>(nt);
   const int max_clusters = sm_count() / 2;  // one CTA per SM (shared memory and all of TMEM), pairs on SM pairs
   const int clusters = p.num_tiles < max_clusters ? p.num_tiles : max_clusters;
-  return launch_maybe_dependent(kern, 2 * clusters, Cfg::NTHREADS, Cfg::SMEM_BYTES, stream, after_prepass, ta, tb_plain,
-                                to, p);
+  return launch_maybe_dependent(kern, dim3(static_cast<unsigned>(2 * clusters)), Cfg::NTHREADS, Cfg::SMEM_BYTES, stream,
+                                after_prepass, ta, tb_plain, to, p);
 }
 
 static int64_t tile_count(int64_t R, int64_t rows, int64_t cols, int bn, int mt) {
@@ -343,7 +356,8 @@ static int auto_variant(int64_t R, int64_t rows, int64_t cols, bool allow_bn256,
 struct Lm2expPlan {
   int bn, mt;   // output columns per tile, 128-row blocks per CTA
   bool pair;    // 256 x 256 tile on a pair of CTAs
-  bool tspair;  // ... by the kernel that keeps the generated operand in tensor memory (variant 2566)
+  bool tspair;  // ... by the kernel that keeps the generated operand in tensor memory (variants 2566, 2567)
+  bool optimistic;  // ... without a pre-pass: stabiliser from the first k-block, exact passes as conditional launches (2567)
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
   bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
   bool promote_tf32;      // plain TF32 over more than kLongContraction terms: accumulator re-summed in chunks
@@ -371,9 +385,12 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     const bool want_pair = stab_mode != 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
-    tile_variant = want_pair ? 2564 : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
+    // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
+    const int pair_variant = precision == TRITURUS_B200_PRECISION_TF32 ? (stab_mode == 0 && !have_m ? 2567 : 2566) : 2564;
+    tile_variant = want_pair ? pair_variant : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
-  const bool tspair = tile_variant == 2566;
+  const bool optimistic = tile_variant == 2567 && stab_mode == 0 && !have_m;
+  const bool tspair = tile_variant == 2566 || tile_variant == 2567;
   if (tspair) {
     if (precision != TRITURUS_B200_PRECISION_TF32) return TRITURUS_B200_EINVAL;
     tile_variant = 2564;  // same tile and stabiliser handling as the other CTA-pair kernel
@@ -396,6 +413,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   out->mt = pair ? 4 : mt;
   out->pair = pair;
   out->tspair = tspair;
+  out->optimistic = optimistic;
   out->fused = fused && !have_m;
   out->colmax_exclusive = !pair && I <= 128 * mt;
   out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
@@ -443,14 +461,14 @@ int triturus_b200_selftest_wait_timeout(int32_t* status_dev, int64_t limit_cycle
   return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
 }
 
-int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
-                             void* stream) {
+static int colmax_run(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
+                      void* stream, const int* only_if, int* publish) {
   if (x == nullptr || m == nullptr || x_strides == nullptr) return TRITURUS_B200_EINVAL;
   if (R <= 0 || J <= 0 || K <= 0 || J > INT32_MAX || K > INT32_MAX) return TRITURUS_B200_EINVAL;
   if (R > 65535) {  // gridDim.y holds the batch: block by block beyond its limit
     for (int64_t r0 = 0; r0 < R; r0 += 65535) {
-      const int rc = triturus_b200_colmax_f32(x + r0 * x_strides[0], m + r0 * K, R - r0 < 65535 ? R - r0 : 65535, J,
-                                              K, x_strides, stream);
+      const int rc = colmax_run(x + r0 * x_strides[0], m + r0 * K, R - r0 < 65535 ? R - r0 : 65535, J, K, x_strides,
+                                stream, only_if, publish);
       if (rc != TRITURUS_B200_OK) return rc;
     }
     return TRITURUS_B200_OK;
@@ -459,14 +477,18 @@ int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int
   const bool vec = (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
   const dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(R));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (vec) {
-    colmax_kernel<true><<<grid, 256, 0, st>>>(x, m, static_cast<int>(J), static_cast<int>(K), x_strides[0],
-                                             x_strides[1]);
-  } else {
-    colmax_kernel<false><<<grid, 256, 0, st>>>(x, m, static_cast<int>(J), static_cast<int>(K), x_strides[0],
-                                              x_strides[1]);
-  }
-  return cudaGetLastError() == cudaSuccess ? TRITURUS_B200_OK : TRITURUS_B200_ELAUNCH;
+  // (a conditional launch follows the optimistic contraction as its programmatic dependent)
+  const bool dep = only_if != nullptr;
+  const int Ji = static_cast<int>(J), Ki = static_cast<int>(K);
+  return vec ? launch_maybe_dependent(colmax_kernel<true>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
+                                      only_if, publish)
+             : launch_maybe_dependent(colmax_kernel<false>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
+                                      only_if, publish);
+}
+
+int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
+                             void* stream) {
+  return colmax_run(x, m, R, J, K, x_strides, stream, nullptr, nullptr);
 }
 
 int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
@@ -476,7 +498,8 @@ int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, in
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
-  return plan.fused ? 1 : 2;
+  // optimistic stabiliser: the contraction and the two conditional launches of the exact passes
+  return plan.fused ? 1 : (plan.optimistic ? 3 : 2);
 }
 
 int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
@@ -486,14 +509,18 @@ int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int pr
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
-  return (plan.fused ? 2 : 1) * 100000 + plan.bn * 10 + (plan.tspair ? 6 : plan.mt);
+  return (plan.fused ? 2 : (plan.optimistic ? 0 : 1)) * 100000 + plan.bn * 10 + (plan.tspair ? (plan.optimistic ? 7 : 6) : plan.mt);
 }
+
+// Workspace layout: [two flag words of the optimistic stabiliser, padded to 256 bytes][R x K stabilisers].
+// A workspace of only R * K floats (the layout before the flags existed) holds the stabilisers at offset 0.
+constexpr size_t kLm2expFlagBytes = 256;
 
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K) {
   (void)I;
   (void)J;
   if (R <= 0 || K <= 0) return 0;
-  return static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float);
+  return kLm2expFlagBytes + static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float);
 }
 
 // Shared body of the lm2exp entry points.  b_colmax (optional): [R, K] column maxima of b supplied by the
@@ -510,7 +537,7 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   if (precision != TRITURUS_B200_PRECISION_TF32 && precision != TRITURUS_B200_PRECISION_3XTF32)
     return TRITURUS_B200_EINVAL;
   if (b_colmax == nullptr &&
-      (workspace == nullptr || workspace_bytes < triturus_b200_lm2exp_workspace_bytes(R, I, J, K) ||
+      (workspace == nullptr || workspace_bytes < static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float) ||
        (reinterpret_cast<uintptr_t>(workspace) & 255) != 0))
     return TRITURUS_B200_EWORKSPACE;
   if (out_colmax != nullptr && (out_colmax == b_colmax || (reinterpret_cast<uintptr_t>(out_colmax) & 3) != 0))
@@ -544,7 +571,11 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   const bool pair = plan.pair, fused = plan.fused;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const float* m_ws = b_colmax != nullptr ? b_colmax : static_cast<const float*>(workspace);
+  const size_t m_bytes = static_cast<size_t>(R) * static_cast<size_t>(K) * sizeof(float);
+  const bool ws_flags = workspace != nullptr && workspace_bytes >= kLm2expFlagBytes + m_bytes;
+  float* m_buf = ws_flags ? reinterpret_cast<float*>(static_cast<char*>(workspace) + kLm2expFlagBytes)
+                          : static_cast<float*>(workspace);
+  const float* m_ws = b_colmax != nullptr ? b_colmax : m_buf;
   int rc = TRITURUS_B200_OK;
   // Column maxima of the result: tiles of several row tiles reduce into the array, which therefore starts
   // at -inf; a single row tile stores every column exactly once and needs no fill.
@@ -621,13 +652,30 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     rc = make_tmap(&tb_plain, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != TRITURUS_B200_OK) return rc;
   }
+  const int64_t bstr[3] = {bs0, bs1, 1};
+  if (use_ts && plan.optimistic && prepass && ws_flags) {
+    // No pre-pass: the contraction takes each column's stabiliser from its first 32 rows and raises the flag
+    // if a result overflowed; the exact pre-pass and contraction follow as launches that return at once
+    // unless the flag is up.  Nothing clears the flag beforehand: the conditional contraction puts it down when
+    // it runs, so a word that is up by accident (fresh memory) costs one exact pass and never a wrong result.
+    int* flag = static_cast<int*>(workspace);
+    Lm2expParams po = p;
+    po.m_ws = nullptr;
+    po.opt_flag = flag;
+    rc = launch_lm2exp_tspair<LmTsPairOpt>(ta, tb_plain, to, po, st, false);
+    if (rc != TRITURUS_B200_OK) return rc;
+    rc = colmax_run(b, m_buf, R, J, K, bstr, stream, flag, flag + 1);
+    if (rc != TRITURUS_B200_OK) return rc;
+    p.only_if = flag + 1;
+    p.reset_flag = flag;
+    return launch_lm2exp_tspair<LmTsPair>(ta, tb_plain, to, p, st, true);
+  }
   if (prepass) {
-    const int64_t bstr[3] = {bs0, bs1, 1};
-    rc = triturus_b200_colmax_f32(b, static_cast<float*>(workspace), R, J, K, bstr, stream);
+    rc = triturus_b200_colmax_f32(b, m_buf, R, J, K, bstr, stream);
     if (rc != TRITURUS_B200_OK) return rc;
   }
   const bool dep = prepass;
-  if (use_ts) return launch_lm2exp_tspair(ta, tb_plain, to, p, st, dep);
+  if (use_ts) return launch_lm2exp_tspair<LmTsPair>(ta, tb_plain, to, p, st, dep);
   if (pair) {
     return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st, dep)
                                                         : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st, dep);
@@ -752,6 +800,7 @@ int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan, have_b_colmax != 0);
   if (rc != TRITURUS_B200_OK) return rc;
+  if (plan.optimistic && !want_out_colmax) return 3;  // as triturus_b200_lm2exp_launches
   return 1 + ((plan.fused || have_b_colmax) ? 0 : 1) + ((want_out_colmax && !plan.colmax_exclusive) ? 1 : 0);
 }
 

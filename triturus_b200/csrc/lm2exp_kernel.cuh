@@ -45,6 +45,10 @@ struct Lm2expParams {
   int a_mn;                 // a is stored with i contiguous (a transposed view): MN-major A operand, loaded as
                             // four 32 i x 32 j boxes per 128-row tile in the layout of the b boxes
   int* status;
+  // Only the TMEM-operand pair kernel reads these two.
+  const int* only_if = nullptr;  // a conditional launch: the kernel returns at once when *only_if == 0
+  int* opt_flag = nullptr;       // optimistic-stabiliser instances set *opt_flag = 1 when a result overflowed
+  int* reset_flag = nullptr;     // a conditional launch that does run puts this word (the flag behind only_if) down
 };
 
 // PLAIN_ = true turns the kernel into a plain batched matrix product out = a * b (the reference's `mm`,

@@ -23,7 +23,8 @@
 //   warp 1      TMEM allocation; in the leader CTA one lane issues the pair MMAs.
 //   warp 2      TMA producer of ring 2: this CTA's 128 columns of b (no swizzle).
 //   warps 4-7   epilogue (TMEM lane quarter = warp % 4).
-//   warps 8-15  transform: two groups of four warps (one per lane quarter) take alternate k-blocks.
+//   warps 8-15  transform: NG = two groups of four warps (one per lane quarter) take alternate k-blocks (three
+//               groups, 20 warps at 96 registers, ran 5 % slower; ring depths 6+6, 5+7, 7+5 instead of 8+4 the same).
 #pragma once
 
 #include "lm2exp_kernel.cuh"
@@ -50,11 +51,11 @@ __device__ long long g_timeline[16 * 256];
 // (1-2 us from L2 / HBM) -> transform -> MMA -> commit" is several thousand cycles long, so the number of
 // k-blocks in flight, not any pipe, bounds a single ring of six stages (measured 1 100 cycles per k-block for
 // 512 cycles of MMAs); two rings put 8 + 5 tiles in flight in the same shared memory.
-template <int NS_, int NSB_>
+template <int NS_, int NSB_, int NG_ = 2, bool OPT_ = false>
 struct Lm2expTsPairCfg {
   static constexpr int BM = 128;   // columns k per CTA (256 per pair): TMEM lanes
   static constexpr int BN = 256;   // rows i per pair tile (N of the MMA), 128 per CTA's shared memory
-  static constexpr int BK = 32, NTW = 8, NS = NS_, NSB = NSB_;
+  static constexpr int BK = 32, NG = NG_, NTW = 4 * NG_, NS = NS_, NSB = NSB_;
   static constexpr int A_TILE = 128 * BK * 4;  // this CTA's rows of a: 16 KB
   static constexpr int B_TILE = BK * BM * 4;   // this CTA's columns of b: 32 rows j x 128 k = 16 KB
   static constexpr int ACC_COLS = BN;
@@ -62,8 +63,15 @@ struct Lm2expTsPairCfg {
   static constexpr int TMEM_COLS = 512;
   static constexpr int NTHREADS = (8 + NTW) * 32;
   static constexpr int EPI_STAGE = 4 * 2 * 32 * 128;  // per epilogue warp two 32 x 32 fp32 boxes
-  static constexpr int NBAR = 3 * NS + 2 * NSB + 2;
-  static constexpr int SMEM_BYTES = 1024 + NS * A_TILE + NSB * B_TILE + EPI_STAGE + NBAR * 8 + 64;
+  // OPT: no stabiliser pre-pass.  The stabiliser of a column is the maximum over its first k-block (32 rows j),
+  // found by the transform warp that handles that k-block and handed to the other roles through shared memory
+  // (two slots of 128 floats, per-quarter barriers).  Later values may exceed it: exp(b - m) then exceeds 1,
+  // which fp32 absorbs up to e^88; a result that overflowed all the same (+inf or NaN) raises *opt_flag and the
+  // caller's conditional launches redo the call with the exact column maxima.
+  static constexpr bool OPT = OPT_;
+  static constexpr int NBAR = 3 * NS + 2 * NSB + 2 + (OPT ? 16 : 0);
+  static constexpr int M_TILE_BYTES = OPT ? 2 * BM * 4 : 0;
+  static constexpr int SMEM_BYTES = 1024 + NS * A_TILE + NSB * B_TILE + EPI_STAGE + M_TILE_BYTES + NBAR * 8 + 64;
   static_assert(E_COL0 + NS * BK <= TMEM_COLS, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
 };
@@ -88,12 +96,23 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                      const __grid_constant__ CUtensorMap tmap_out, const Lm2expParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, NS = Cfg::NS, NSB = Cfg::NSB;
 
+  // A conditional launch: runs only if the launch before it raised the flag (same value for every thread of
+  // both CTAs, read before any barrier or allocation exists).
+  if (p.only_if != nullptr) {
+    pdl_wait();  // the conditional pre-pass before this launch has republished the flag in *only_if
+    if (*p.only_if == 0) return;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.reset_flag != nullptr) *p.reset_flag = 0;  // all its readers are done
+  }
+  // Optimistic instances let the conditional launches behind them take their places as this grid's CTAs leave.
+  if (Cfg::OPT) pdl_launch_dependents();
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_base = smem;                     // ring 1: NS tiles of a
   uint8_t* b_base = smem + NS * Cfg::A_TILE;  // ring 2: NSB tiles of b
   uint8_t* epi_stage = b_base + NSB * Cfg::B_TILE;  // 4 warps x 4 KB staging boxes, 1024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_STAGE);
+  float* m_tile = reinterpret_cast<float*>(epi_stage + Cfg::EPI_STAGE);  // OPT: [2][BM] stabilisers of two tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + Cfg::EPI_STAGE + Cfg::M_TILE_BYTES);
   uint64_t* a_full = bars;                // [NS] this CTA's tile of a landed
   uint64_t* xf_done = bars + NS;          // [NS] (leader's copy is used) E^T stage written and a landed, both CTAs
   uint64_t* stage_empty = bars + 2 * NS;  // [NS] pair MMAs reading ring-1 stage retired (committed by the leader)
@@ -101,7 +120,9 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint64_t* b_empty = b_full + NSB;       // [NSB] the four transform warps of the k-block hold it in registers
   uint64_t* acc_full = b_empty + NSB;     // [1] accumulator complete (committed by the leader)
   uint64_t* acc_empty = acc_full + 1;     // [1] (leader's copy is used) epilogues of both CTAs drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* m_ready = acc_empty + 1;      // OPT [2][4] slot, lane quarter: stabilisers written
+  uint64_t* m_free = m_ready + 8;         // OPT [2][4] every reader of the quarter (epilogue warp, other groups) is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1 + (Cfg::OPT ? 16 : 0));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -126,6 +147,12 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 8);
+    if (Cfg::OPT) {
+      for (int i = 0; i < 8; ++i) {
+        mbar_init(&m_ready[i], 1);
+        mbar_init(&m_free[i], Cfg::NG);  // the epilogue warp and one warp of every other transform group
+      }
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -242,17 +269,28 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     pdl_wait();  // m comes from the pre-pass, which may still be running when this kernel starts
     uint32_t tcount = 0;
     bool ok = true;
+    bool overflowed = false;  // OPT: some result of this lane came out +inf or NaN
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
       const int k0 = n0 + static_cast<int>(rank) * BM + q * 32;  // first column of this warp's 32
       const int kcol = k0 + lane;
       const bool col_ok = kcol < p.K;
-      const float m = col_ok ? clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol)) : 0.f;
+      float m = 0.f;
+      if (!Cfg::OPT && col_ok) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
       float* ocol = p.out + static_cast<int64_t>(r) * p.out_s0 + kcol;
       if (!(ok = mbar_wait_warp(acc_full, tcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
       if (warp == 4 && lane == 0) TB200_TL(7, tcount);
       tc_fence_after_sync();
+      if (Cfg::OPT) {
+        // the stabilisers this tile was computed with (written long before the accumulator completed)
+        const uint32_t slot = (tcount & 1) * 4 + q;
+        if (!(ok = mbar_wait_warp(&m_ready[slot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
+        const float mt = m_tile[(tcount & 1) * BM + q * 32 + lane];
+        m = col_ok ? mt : 0.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&m_free[slot]);
+      }
       const int nchunks = (k0 < p.K) ? min(BN / 32, (p.I - i0 + 31) / 32) : 0;
       if (nchunks == 0) {
         // nothing to store (this warp's columns are padding): release the accumulator right away
@@ -291,6 +329,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 const float o = m + lg2_approx(__uint_as_float(v[h][e])) * LN2_F;
+                if (Cfg::OPT) overflowed |= !(o < INFINITY);
                 *reinterpret_cast<float*>(stg + sw128_offset(e, lane)) = o;
               }
               fence_proxy_async_smem();
@@ -306,6 +345,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 const float o = m + lg2_approx(__uint_as_float(v[h][e])) * LN2_F;
+                if (Cfg::OPT) overflowed |= !(o < INFINITY);
                 if (col_ok && e < nrows) orow[static_cast<int64_t>(e) * p.out_s1] = o;
               }
             }
@@ -315,23 +355,36 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (warp == 4 && lane == 0) TB200_TL(8, tcount);
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
+    if (Cfg::OPT) {
+      if (__any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
+    }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: b tile -> E^T in tensor memory
     const int q = warp & 3;         // TMEM lane quarter this warp may write
-    const int grp = (warp - 8) >> 2;  // this warp's group takes the k-blocks with kb % 2 == grp
+    const int grp = (warp - 8) >> 2;  // this warp's group takes the k-blocks with kb % NG == grp
     const int kl = q * 32 + lane;
     const uint32_t ebase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::E_COL0;
     const uint32_t xf_done_leader0 = map_to_cta(smem_u32(&xf_done[0]), 0);
     pdl_wait();  // m comes from the pre-pass (the producer warp is already loading operand tiles meanwhile)
-    uint32_t it0 = 0;
+    uint32_t it0 = 0, tcount = 0;
     bool ok = true;
-    for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+    for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
       const int kcol = n0 + static_cast<int>(rank) * BM + kl;
       // A column past K reads zero-filled values; the stabiliser +inf turns them into exact zeros.
-      const float m = (kcol < p.K) ? clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol)) : INFINITY;
-      for (int kb = grp; kb < KB; kb += 2) {
+      float m = INFINITY;
+      if (!Cfg::OPT && kcol < p.K) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
+      const uint32_t mslot = (tcount & 1) * 4 + q;
+      float* mdst = m_tile + (tcount & 1) * BM + kl;
+      if (Cfg::OPT && grp != 0) {
+        // the group of k-block 0 publishes the tile's stabilisers
+        if (!(ok = mbar_wait_warp(&m_ready[mslot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        m = *mdst;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&m_free[mslot]);
+      }
+      for (int kb = grp; kb < KB; kb += Cfg::NG) {
         const uint32_t it = it0 + static_cast<uint32_t>(kb);
         const int s = it % NS;
         const uint32_t ph = (it / NS) & 1;
@@ -343,6 +396,19 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int x = 0; x < 32; ++x) v[x] = col[x * BM];
         const int jrem = p.J - kb * BK;
+        if (Cfg::OPT && kb == 0) {
+          // (grp == 0) stabiliser = maximum over the first k-block; the slot's readers of two tiles ago are done
+          float mx = -INFINITY;
+#pragma unroll
+          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, x < jrem ? v[x] : -INFINITY);
+          m = (kcol < p.K) ? clamp_stab(mx) : INFINITY;
+          if (tcount >= 2) {
+            if (!(ok = mbar_wait_warp(&m_free[mslot], ((tcount >> 1) - 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          }
+          *mdst = m;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&m_ready[mslot]);
+        }
         uint32_t e[32];
         if (jrem >= BK) {
 #pragma unroll
