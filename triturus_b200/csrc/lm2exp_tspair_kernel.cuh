@@ -22,6 +22,7 @@
 //   warp 0      TMA producer of ring 1: this CTA's 128 rows of a (128B swizzle).
 //   warp 1      TMEM allocation; in the leader CTA one lane issues the pair MMAs.
 //   warp 2      TMA producer of ring 2: this CTA's 128 columns of b (no swizzle).
+//   warp 3      watches the a tiles land and says so on the leader's xf_done barriers.
 //   warps 4-7   epilogue (TMEM lane quarter = warp % 4).
 //   warps 8-15  transform: NG = two groups of four warps (one per lane quarter) take alternate k-blocks (three
 //               groups, 20 warps at 96 registers, ran 5 % slower; ring depths 6+6, 5+7, 7+5 instead of 8+4 the same).
@@ -138,7 +139,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&xf_done[s], 2 * 4);  // four warps (one per lane quarter) in each CTA
+      mbar_init(&xf_done[s], 2 * 4 + 2);  // four transform warps (one per lane quarter) and the a-tile watcher, in each CTA
       mbar_init(&stage_empty[s], 1);
     }
     for (int s = 0; s < NSB; ++s) {
@@ -255,6 +256,23 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
         if (ok) umma_commit_pair_mcast(smem_u32(acc_full), 3);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ a-tile watcher
+    // The leader's MMA thread reads both CTAs' tiles of a and waits only on xf_done: this lane adds "this CTA's
+    // tile of a has landed" to that barrier, so that the transform warps need not wait for it in their chain.
+    if (lane == 0) {
+      const uint32_t xf_done_leader0 = map_to_cta(smem_u32(&xf_done[0]), 0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % NS;
+          if (!(ok = mbar_wait(&a_full[s], (it / NS) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          mbar_arrive_cluster(xf_done_leader0 + static_cast<uint32_t>(s) * 8u);
+        }
       }
     }
     __syncwarp();
@@ -421,13 +439,10 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // Every lane has consumed its values of the b tile: hand the tile back to its producer.
         __syncwarp();
         if (lane == 0) mbar_arrive(&b_empty[sb]);
-        // The E^T stage is free once the MMAs that read it last time have retired; the tile of a that the same
-        // MMAs will read must have landed before the leader is told that the stage is ready (the leader's MMA
-        // thread reads both CTAs' tiles and waits for nothing else).
+        // The E^T stage is free once the MMAs that read it last time have retired.  (That the tile of a the same
+        // MMAs will read has landed is the watcher warp's part of xf_done.)
         if (!(ok = mbar_wait_warp(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
         if (warp == 8 && lane == 0) TB200_TL(4, it);
-        if (!(ok = mbar_wait_warp(&a_full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
-        if (warp == 8 && lane == 0) TB200_TL(5, it);
         tc_fence_after_sync();
         tmem_st_32x32(ebase + s * BK, e);
         tmem_st_wait();
