@@ -5,7 +5,11 @@
  * All tensor pointers are DEVICE pointers to fp32 data on the device that is current when the call is
  * made.  Strides are in elements.  The innermost stride of every tensor must be 1, every other stride a
  * multiple of 4 elements and every base pointer 16-byte aligned (TMA rules); callers that cannot meet this
- * make a padded copy first (the Python wrappers do).  The library allocates nothing: the output, the
+ * make a padded copy first (the Python wrappers do).  Exception: the operands a and b of lm2exp may also be
+ * transposed views (a with i contiguous, b with j contiguous; the stride-1 dimension swapped, the other rules
+ * unchanged), which the kernels read in place; a b of that kind runs on the single-CTA tiles with the pre-pass
+ * stabiliser, and variant codes asking for a pair tile or the fused max pass are refused for it.  The library
+ * allocates nothing: the output, the
  * workspace and the status word belong to the caller.  Calls are asynchronous on `stream` and never
  * synchronise; they are re-entrant and may run concurrently on different streams or devices as long as
  * each in-flight call has its own workspace and output.

@@ -392,6 +392,67 @@ def test_transposed_a_with_odd_rows_falls_back_to_a_copy():
     _assert_close(got.cpu(), a_t.transpose(1, 2).contiguous(), b, "3xtf32")
 
 
+@pytest.mark.parametrize("variant", [0, 1281, 1282, 2561, 2562, 101282])
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("shape", [(2, 130, 100, 260), (3, 257, 36, 516), (1, 64, 1028, 130), (2, 7, 64, 5),
+                                   (4, 512, 512, 512)])
+def test_transposed_b_is_read_in_place(shape, precision, variant):
+    """b given as a transposed view (j contiguous, e.g. the transpose of a contiguous [R, K, J] tensor;
+    triturus/lm2exp.py:190-198 forwards any strides): the single-CTA kernel uses it as a K-major operand without a
+    copy, with the row maxima of the stored tensor as stabiliser.  Ragged shapes, isolated -inf entries and an
+    all -inf column."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    R, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + variant)
+    a = torch.rand(R, I, J, generator=g)
+    b_t = torch.randn(R, K, J, generator=g) * 6.0 + 50.0 * torch.randn(R, K, 1, generator=g)  # stored [R, K, J]
+    b_t[0, min(3, K - 1), :] = float("-inf")
+    b_t[torch.rand(R, K, J, generator=g) < 0.01] = float("-inf")
+    b_view = b_t.cuda().transpose(1, 2)  # logical [R, J, K], stride 1 along j
+    assert _native._lm2exp_b_operand(b_view, variant).data_ptr() == b_view.data_ptr()
+    got = tb.lm2exp(a.cuda(), b_view, precision=precision, variant=variant)
+    tb.check_status()
+    assert torch.all(got[0, :, min(3, K - 1)] == float("-inf"))
+    _assert_close(got.cpu(), a, b_t.transpose(1, 2).contiguous(), precision)
+
+
+def test_transposed_b_special_cases():
+    """A pair tile or the fused max pass asked for by variant code, or a j extent that is not a multiple of 4
+    (the k stride of the view then breaks the tensor-map rules): the wrapper makes the copy; the C ABI refuses the
+    combination it cannot run.  Both operands transposed at once work in place."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(13)
+    a = torch.rand(2, 300, 64, generator=g)
+    b_t = torch.randn(2, 520, 64, generator=g) * 4.0
+    b_view = b_t.cuda().transpose(1, 2)
+    for variant in (2564, 202561):
+        assert _native._lm2exp_b_operand(b_view, variant).data_ptr() != b_view.data_ptr()
+        got = tb.lm2exp(a.cuda(), b_view, precision="tf32", variant=variant)
+        tb.check_status()
+        _assert_close(got.cpu(), a, b_t.transpose(1, 2).contiguous(), "tf32")
+    b_odd = torch.randn(2, 130, 50, generator=g)  # J = 50
+    a_odd = torch.rand(2, 40, 50, generator=g)
+    got = tb.lm2exp(a_odd.cuda(), b_odd.cuda().transpose(1, 2), precision="3xtf32")
+    tb.check_status()
+    _assert_close(got.cpu(), a_odd, b_odd.transpose(1, 2).contiguous(), "3xtf32")
+    a_t = torch.rand(2, 64, 300, generator=g)  # stored [R, J, I]
+    got = tb.lm2exp(a_t.cuda().transpose(1, 2), b_view, precision="3xtf32")
+    tb.check_status()
+    _assert_close(got.cpu(), a_t.transpose(1, 2).contiguous(), b_t.transpose(1, 2).contiguous(), "3xtf32")
+    # C ABI: a pair tile with a K-major b is an invalid combination
+    R, I, J, K = 2, 300, 64, 520
+    ad, out = a.cuda(), torch.empty(R, I, K, device="cuda")
+    ws = torch.zeros(R * K + 64, device="cuda")
+    rc = _native.LIB.triturus_b200_lm2exp_f32(
+        ad.data_ptr(), b_view.data_ptr(), out.data_ptr(), R, I, J, K, _native._i64(ad.stride()),
+        _native._i64(b_view.stride()), _native._i64(out.stride()), 0, 2564, ws.data_ptr(), ws.numel() * 4, None, None)
+    assert rc == -1, rc  # TRITURUS_B200_EINVAL
+
+
 def test_batches_beyond_the_grid_limit():
     """More than 65535 batch entries (the reference's 1-D grid takes any batch, triturus/lm2exp.py:177-181): the
     library runs them in blocks of 65535 on the same stream."""

@@ -250,6 +250,19 @@ def _lm2exp_a_operand(a: torch.Tensor, K: int) -> torch.Tensor:
     return _tma_ready(a)
 
 
+def _lm2exp_b_operand(b: torch.Tensor, variant: int) -> torch.Tensor:
+    """b as the kernel takes it.  A transposed view (j contiguous, e.g. `x.transpose(1, 2)` of a contiguous x)
+    that meets the tensor-map rules is read in place as a K-major operand by the single-CTA kernel, with the
+    pre-pass stabiliser; variant codes that ask for a pair tile or the fused max pass get a copy instead."""
+    R, J, K = b.shape
+    tile, stab = int(variant) % 100000, int(variant) // 100000
+    if K > 1 and b.stride(2) != 1 and (J == 1 or b.stride(1) == 1) and b.data_ptr() % 16 == 0:
+        ok = b.stride(2) > 0 and b.stride(2) % 4 == 0 and (R == 1 or (b.stride(0) > 0 and b.stride(0) % 4 == 0))
+        if ok and tile in (0, 1281, 1282, 2561, 2562) and stab != 2:
+            return b
+    return _tma_ready(b)
+
+
 def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
     """Return `t` or a contiguous copy when its innermost stride is not 1 or a stride is not positive."""
     if (t.shape[-1] == 1 or t.stride(-1) == 1) and all(
@@ -301,7 +314,7 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     R, I, J = a.shape
     K = b.shape[2]
     a = _lm2exp_a_operand(a, K)
-    b = _tma_ready(b)
+    b = _lm2exp_b_operand(b, variant)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
     with _on_device(a.device) as idx:
@@ -325,7 +338,7 @@ def _lm2exp_chain_impl(
     R, I, J = a.shape
     K = b.shape[2]
     a = _lm2exp_a_operand(a, K)
-    b = _tma_ready(b)
+    b = _lm2exp_b_operand(b, variant)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     out_colmax = torch.empty((R, K) if want_colmax else (0,), dtype=torch.float32, device=a.device)
     if b_colmax is not None:

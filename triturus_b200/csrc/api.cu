@@ -88,6 +88,32 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
   }
 }
 
+// The same stabiliser for a b stored with j contiguous (a transposed view): m[r,k] = clamp(max_j x[r,k,j]), one warp
+// per row of J consecutive values, eight rows per block.
+__global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
+                                                      int64_t s0, int64_t sk) {
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k = blockIdx.x * 8 + warp;
+  const int r = blockIdx.y;
+  if (k >= K) return;
+  const float* row = x + static_cast<int64_t>(r) * s0 + static_cast<int64_t>(k) * sk;
+  float mx = -INFINITY;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int J4 = J & ~3;
+    for (int j = lane * 4; j < J4; j += 128) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(row + j));
+      mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
+    for (int j = J4 + lane; j < J; j += 32) mx = fmaxf(mx, __ldg(row + j));
+  } else {
+    for (int j = lane; j < J; j += 32) mx = fmaxf(mx, __ldg(row + j));
+  }
+#pragma unroll
+  for (int sh = 16; sh >= 1; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+  if (lane == 0) m[static_cast<int64_t>(r) * K + k] = clamp_stab(mx);
+}
+
 // Fills m[0..n) with -inf: the start value of the column maxima that an epilogue folds into it.
 __global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* __restrict__ m, int64_t n) {
   for (int64_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) m[i] = -INFINITY;
@@ -368,8 +394,9 @@ struct Lm2expPlan {
 constexpr int64_t kLongContraction = 32768;
 
 // have_m: the caller supplies the stabiliser, so the tile is chosen as usual but no max pass of either kind runs.
+// b_km: b is stored with j contiguous; only the single-CTA kernel takes it, with the pre-pass stabiliser.
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
-                       bool have_m = false) {
+                       bool have_m = false, bool b_km = false) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
   const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
   int tile_variant = variant % 100000;
@@ -382,13 +409,15 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
-    const bool want_pair = stab_mode != 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
+    const bool want_pair = !b_km && stab_mode != 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
     const int pair_variant = precision == TRITURUS_B200_PRECISION_TF32 ? (stab_mode == 0 && !have_m ? 2567 : 2566) : 2564;
     tile_variant = want_pair ? pair_variant : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
+  if (b_km && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567 || stab_mode == 2))
+    return TRITURUS_B200_EINVAL;
   const bool optimistic = tile_variant == 2567 && stab_mode == 0 && !have_m;
   const bool tspair = tile_variant == 2566 || tile_variant == 2567;
   if (tspair) {
@@ -405,7 +434,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   // the whole problem is less than one wave of tiles: a second launch then costs more than the row tiles of a
   // slab each scanning it (cfg1: 18.5 us against 21.7 us).
   const bool one_wave = tile_count(R, I, K, bn, mt) <= sm_count();
-  const bool fused = !pair && (stab_mode == 2 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
+  const bool fused = !pair && !b_km && (stab_mode == 2 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
   // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
   // double-buffered so that the epilogue overlaps the next tile.
   if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
@@ -546,7 +575,11 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
   int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
   int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
-  if ((K > 1 && bs2 != 1) || (K > 1 && os2 != 1)) return TRITURUS_B200_EALIGN;
+  // b with k contiguous is an MN-major tensor-core operand; a transposed view (j contiguous) is used in place as
+  // a K-major operand by the single-CTA kernel.
+  const bool b_km = K > 1 && bs2 != 1;
+  if (b_km && J > 1 && bs1 != 1) return TRITURUS_B200_EALIGN;
+  if (K > 1 && os2 != 1) return TRITURUS_B200_EALIGN;
   if (!aligned16(a) || !aligned16(b)) return TRITURUS_B200_EALIGN;
   // a with j contiguous is a K-major tensor-core operand; a transposed view (i contiguous) is used in place
   // as an MN-major operand.
@@ -557,14 +590,18 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   } else if (!fix_stride(I, as1, round_up4(J)) || !fix_stride(R, as0, round_up4(J) * I)) {
     return TRITURUS_B200_EALIGN;
   }
-  if (!fix_stride(J, bs1, round_up4(K)) || !fix_stride(R, bs0, round_up4(K) * J)) return TRITURUS_B200_EALIGN;
+  if (b_km) {
+    if (!fix_stride(K, bs2, round_up4(J)) || !fix_stride(R, bs0, round_up4(J) * K)) return TRITURUS_B200_EALIGN;
+  } else if (!fix_stride(J, bs1, round_up4(K)) || !fix_stride(R, bs0, round_up4(K) * J)) {
+    return TRITURUS_B200_EALIGN;
+  }
   if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
   if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
 
   Lm2expPlan plan;
   {
     // A supplied stabiliser makes every max pass redundant (and a fused max pass cannot be requested as well).
-    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan, b_colmax != nullptr);
+    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan, b_colmax != nullptr, b_km);
     if (prc != TRITURUS_B200_OK) return prc;
   }
   const int bn = plan.bn, mt = plan.mt;
@@ -602,7 +639,13 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     rc = make_tmap(&ta, a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TRITURUS_B200_OK) return rc;
   }
-  {
+  if (b_km) {
+    const int64_t dims[3] = {J, K, R};
+    const int64_t strides[3] = {1, bs2, bs0};
+    const uint32_t box[3] = {32, static_cast<uint32_t>(bn), 1};
+    rc = make_tmap(&tb, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TRITURUS_B200_OK) return rc;
+  } else {
     const int64_t dims[3] = {K, J, R};
     const int64_t strides[3] = {1, bs1, bs0};
     const uint32_t box[3] = {32, 32, 1};
@@ -627,6 +670,7 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   Lm2expParams p;
   p.out_tma = out_tma ? 1 : 0;
   p.a_mn = a_mn ? 1 : 0;
+  p.b_km = b_km ? 1 : 0;
   p.m_ws = m_ws;
   p.out = out;
   p.out_max = out_colmax;
@@ -670,7 +714,13 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     p.reset_flag = flag;
     return launch_lm2exp_tspair<LmTsPair>(ta, tb_plain, to, p, st, true);
   }
-  if (prepass) {
+  if (prepass && b_km) {
+    for (int64_t r0 = 0; r0 < R; r0 += 65535) {  // (R <= 65535 here: one round)
+      const dim3 grid(static_cast<unsigned>((K + 7) / 8), static_cast<unsigned>(std::min<int64_t>(65535, R - r0)));
+      rowmax_kernel<<<grid, 256, 0, st>>>(b + r0 * bs0, m_buf + r0 * K, static_cast<int>(J), static_cast<int>(K), bs0, bs2);
+    }
+    if (cudaGetLastError() != cudaSuccess) return TRITURUS_B200_ELAUNCH;
+  } else if (prepass) {
     rc = triturus_b200_colmax_f32(b, m_buf, R, J, K, bstr, stream);
     if (rc != TRITURUS_B200_OK) return rc;
   }

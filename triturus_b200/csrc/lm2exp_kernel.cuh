@@ -44,6 +44,8 @@ struct Lm2expParams {
   int out_tma;              // out meets the TMA rules: the epilogue stores through tmap_out
   int a_mn;                 // a is stored with i contiguous (a transposed view): MN-major A operand, loaded as
                             // four 32 i x 32 j boxes per 128-row tile in the layout of the b boxes
+  int b_km = 0;             // b is stored with j contiguous (a transposed view): K-major B operand, one 32 j x BN k
+                            // box per stage in the 128-byte swizzle, exp'd in place row by row; pre-pass stabiliser only
   int* status;
   // Only the TMEM-operand pair kernel reads these two.
   const int* only_if = nullptr;  // a conditional launch: the kernel returns at once when *only_if == 0
@@ -225,9 +227,13 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
               }
             }
+            if (p.b_km) {
+              tma_load_3d(b_tile(s, 0), &tmap_b, &full[s], kb * BK, n0, r);  // rows k of 32 j: the layout of an a tile
+            } else {
 #pragma unroll
-            for (int g = 0; g < NGRP; ++g)
-              tma_load_3d(b_tile(s, 0) + g * Cfg::B_BOX, &tmap_b, &full[s], n0 + g * 32, kb * BK, r);
+              for (int g = 0; g < NGRP; ++g)
+                tma_load_3d(b_tile(s, 0) + g * Cfg::B_BOX, &tmap_b, &full[s], n0 + g * 32, kb * BK, r);
+            }
           }
         }
       }
@@ -237,8 +243,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // B operand is MN-major; A too when a is a transposed view (bit 15)
-      const uint32_t idesc = umma_idesc_tf32(BM, BN) | (1u << 16) | (p.a_mn ? (1u << 15) : 0u);
+      const uint32_t idesc = umma_idesc_tf32(BM, BN) | (p.b_km ? 0u : (1u << 16)) | (p.a_mn ? (1u << 15) : 0u);
       const uint32_t a_step = p.a_mn ? 64u : 2u;  // encoded address step per 8 contraction values
+      const uint32_t b_step = p.b_km ? 2u : 64u;  // K-major: 32 bytes along the row; MN-major: eight 128-byte rows
       uint32_t it = 0, ccount = 0;  // k-block stages and accumulation chunks issued so far
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -266,8 +273,11 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             if (!(ok = mbar_wait(&full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
             if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
             tc_fence_after_sync();
-            const uint64_t db_hi = umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
-            const uint64_t db_lo = PREC ? umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX) : 0;
+            const uint64_t db_hi = p.b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 0)))
+                                          : umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
+            const uint64_t db_lo = !PREC ? 0
+                                   : p.b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 1)))
+                                            : umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX);
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
               const uint32_t d = tmem_base + buf * Cfg::ACC_COLS + t * BN;
@@ -282,11 +292,11 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 // 128-byte rows (two 512-byte swizzle atoms) of the MN-major B boxes.
                 const uint32_t acc = (kb > kb0 || ks > 0) ? 1u : 0u;
                 if (PREC) {
-                  umma_tf32_ss(d, da_hi + a_step * ks, db_lo + 64 * ks, idesc, acc);
-                  umma_tf32_ss(d, da_lo + a_step * ks, db_hi + 64 * ks, idesc, 1u);
-                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_lo + b_step * ks, idesc, acc);
+                  umma_tf32_ss(d, da_lo + a_step * ks, db_hi + b_step * ks, idesc, 1u);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + b_step * ks, idesc, 1u);
                 } else {
-                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + 64 * ks, idesc, acc);
+                  umma_tf32_ss(d, da_hi + a_step * ks, db_hi + b_step * ks, idesc, acc);
                 }
               }
             }
@@ -495,6 +505,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       decode(tile, r, n0, i0);
       const int col0 = n0 + grp * 32 + c * 4;  // first of this thread's 4 columns
       float m4[4];
+      // K-major b: a thread owns CPT 16-byte pieces of one row k of the tile (consecutive lanes, consecutive rows).
+      constexpr int TPR = Cfg::NTT / BN, CPT = 8 / TPR;
+      const int krow = tt % BN, kpart = tt / BN;
 
       if (fused) {
         // ---- max pass: running maximum of this thread's 4 columns over its row slots
@@ -553,6 +566,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       } else if (Cfg::PLAIN) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) m4[x] = 0.f;  // plain product: no stabiliser
+      } else if (p.b_km) {
+        m4[0] = (n0 + krow < p.K) ? clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + n0 + krow)) : 0.f;
+        m4[1] = m4[2] = m4[3] = m4[0];
       } else {
         const float* mrow = p.m_ws + static_cast<int64_t>(r) * p.K;
 #pragma unroll
@@ -561,7 +577,12 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
       // publish the stabiliser of this tile's columns for the epilogue
       const int slot = tcount & 1;
-      if (rp == 0) {
+      if (p.b_km) {
+        if (kpart == 0) {  // (whole warps: BN is a multiple of 32)
+          if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          msum[slot * BN + krow] = m4[0];
+        }
+      } else if (rp == 0) {
         if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
         if (jsub == 0)
           *reinterpret_cast<float4*>(msum + slot * BN + grp * 32 + c * 4) = make_float4(m4[0], m4[1], m4[2], m4[3]);
@@ -579,6 +600,46 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         uint8_t* box_lo = b_tile(s, PREC ? 1 : 0) + grp * Cfg::B_BOX;
         const int jrem = p.J - kb * BK;
         constexpr int NLD = Cfg::ROWS_PER_WARP / 4;
+        if (p.b_km) {
+          // Row krow of the tile is column n0 + krow of b with its 32 values j of this k-block: eight 16-byte
+          // pieces, piece i at (i ^ (krow & 7)) * 16 of the 128-byte row.  Eight consecutive lanes read the same
+          // piece index of eight consecutive rows, which the swizzle spreads over all 32 banks.
+          uint8_t* rowp_hi = b_tile(s, 0) + krow * 128;
+          uint8_t* rowp_lo = b_tile(s, PREC ? 1 : 0) + krow * 128;
+          const bool kv = n0 + krow < p.K;
+          float4 w[CPT];
+#pragma unroll
+          for (int x = 0; x < CPT; ++x)
+            w[x] = *reinterpret_cast<const float4*>(rowp_hi + (((kpart * CPT + x) ^ (krow & 7)) << 4));
+          uint4 whi[CPT];
+          float4 wlo[CPT];
+#pragma unroll
+          for (int x = 0; x < CPT; ++x) {
+            const int j0 = (kpart * CPT + x) * 4;
+            float e[4];
+            e[0] = exp_shifted((kv && j0 + 0 < jrem) ? w[x].x : -INFINITY, m4[0]);
+            e[1] = exp_shifted((kv && j0 + 1 < jrem) ? w[x].y : -INFINITY, m4[0]);
+            e[2] = exp_shifted((kv && j0 + 2 < jrem) ? w[x].z : -INFINITY, m4[0]);
+            e[3] = exp_shifted((kv && j0 + 3 < jrem) ? w[x].w : -INFINITY, m4[0]);
+            if (PREC) {
+              float4 h;
+              tf32_split_rn(e[0], h.x, wlo[x].x);
+              tf32_split_rn(e[1], h.y, wlo[x].y);
+              tf32_split_rn(e[2], h.z, wlo[x].z);
+              tf32_split_rn(e[3], h.w, wlo[x].w);
+              whi[x] = make_uint4(__float_as_uint(h.x), __float_as_uint(h.y), __float_as_uint(h.z), __float_as_uint(h.w));
+            } else {
+              whi[x] = make_uint4(tf32_round_bits(e[0]), tf32_round_bits(e[1]), tf32_round_bits(e[2]),
+                                  tf32_round_bits(e[3]));
+            }
+          }
+#pragma unroll
+          for (int x = 0; x < CPT; ++x) {
+            const uint32_t off = static_cast<uint32_t>(((kpart * CPT + x) ^ (krow & 7)) << 4);
+            *reinterpret_cast<uint4*>(rowp_hi + off) = whi[x];
+            if (PREC) *reinterpret_cast<float4*>(rowp_lo + off) = wlo[x];
+          }
+        } else {
         // All loads first, then the arithmetic, then all stores: the stores go to the addresses the loads
         // came from, so the compiler would otherwise serialise the iterations.
         float4 v[NLD];
@@ -629,6 +690,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           *reinterpret_cast<uint4*>(box_hi + off) = hi[x];
           if (PREC) *reinterpret_cast<float4*>(box_lo + off) = lo[x];
         }
+        }  // (MN-major b)
         if (PREC) {
           // Split the a-tiles in place: hi keeps the tf32 bits, lo = a - hi goes to the second copy.
           float4* ah = reinterpret_cast<float4*>(a_tile(s, 0, 0));
