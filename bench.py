@@ -625,7 +625,9 @@ def main() -> None:
     # with the column maxima supplied (it is then the only launch of the call) and the pre-pass by itself.
     n_launch = launches_per_step(wl, args.precision, args.variant, args.chain)
     kernel_ms = prepass_ms = None
-    if wl.op == "lm2exp" and n_launch in (2, 3) and not args.chain and not args.profile_mode:
+    pcode = plan_code(wl, args.precision, args.variant)
+    stab = pcode // 100000 if wl.op == "lm2exp" else -1  # 0 optimistic pair kernel, 1 pre-pass, 2 / 3 fused max pass
+    if stab in (0, 1) and not args.chain and not args.profile_mode:
         m_pre = tb.colmax(inputs[1])
         kern = lambda: tb.lm2exp(*inputs, precision=args.precision, variant=args.variant, b_colmax=m_pre)  # noqa: E731
         for _ in range(3):
@@ -800,9 +802,11 @@ def main() -> None:
         roof["kernels_per_step"] = n_launch
         roof["kernel"] = ("lt2exp_kernel" if wl.op == "lt2exp" else
                           "lm2exp chain link (stabiliser supplied, column maxima returned)" if args.chain else
-                          ("colmax_kernel + lm2exp_pair_kernel / lm2exp_kernel" if n_launch == 2 else
+                          ("colmax_kernel + lm2exp_pair_kernel / lm2exp_kernel" if stab == 1 else
                            "lm2exp_tspair_kernel with the optimistic stabiliser (+ two conditional launches of the exact "
-                           "passes, which return at once)" if n_launch == 3
+                           "passes, which return at once)" if stab == 0 else
+                           "lm2exp_kernel, max pass over the first k-block of each slab (+ flag hand-over and the "
+                           "conditional launch of the full pass, which returns at once)" if stab == 3
                            else "lm2exp_kernel (fused max pass)"))
         if kernel_ms is not None:
             dom = roofline_of(wl, kernel_ms, peaks, clocks)

@@ -146,6 +146,73 @@ def test_optimistic_stabiliser_is_the_automatic_choice_for_tf32_pairs():
     assert L.triturus_b200_lm2exp_chain_launches(32, 1024, 1024, 1024, 0, 0, 1, 0) == 1
 
 
+def _optimistic_fused_cases():
+    g = torch.Generator().manual_seed(3000)
+    rnd = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    uni = lambda *s: torch.rand(*s, generator=g)  # noqa: E731
+    b = rnd(3, 250, 700) * 6.0 + 50.0 * rnd(3, 1, 700)
+    b[0, :, 3] = float("-inf")
+    b[uni(3, 250, 700) < 0.01] = float("-inf")
+    yield "random", uni(3, 200, 250), b, False
+    b = torch.arange(512, dtype=torch.float32).view(1, 512, 1).expand(2, 512, 300).contiguous() + rnd(2, 512, 300)
+    yield "ramp-of-500", uni(2, 100, 512), b, True
+    b = rnd(2, 256, 300)
+    b[:, :32] = float("-inf")
+    yield "first-rows-all-neg-inf", uni(2, 256, 256), b, True
+    b = rnd(2, 256, 300)
+    b[:, 64:] += 60.0
+    yield "later-rows-60-above", uni(2, 256, 256) * 1e-3, b, False
+
+
+@pytest.mark.parametrize("tile", [0, 1281, 1282, 2561])
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("case", list(_optimistic_fused_cases()), ids=lambda c: c[0])
+def test_optimistic_fused_max_pass(case, precision, tile):
+    """Stabiliser code 3: the fused max pass of the single-CTA kernel scans the first k-block of a slab only; a
+    result that overflowed makes the conditional launch behind it redo the call with the full pass (code 2), whose
+    result it then equals bit for bit."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    name, a, b, exact = case
+    if precision == "3xtf32" and tile == 2561:
+        pytest.skip("3xTF32 tiles have 128 columns")
+    R, I, J = a.shape
+    K = b.shape[2]
+    prec = 0 if precision == "tf32" else 1
+    assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, prec, 300000 + tile) // 100000 == 3
+    assert _native.LIB.triturus_b200_lm2exp_launches(R, I, J, K, prec, 300000 + tile) == 3
+    ad, bd = a.cuda(), b.cuda()
+    got = tb.lm2exp(ad, bd, precision=precision, variant=300000 + tile)
+    tb.check_status()
+    _assert_close(got.cpu(), a, b, precision)
+    full = tb.lm2exp(ad, bd, precision=precision, variant=200000 + tile)
+    tb.check_status()
+    assert torch.equal(torch.isinf(got), torch.isinf(full))
+    if exact:
+        assert torch.equal(got, full)
+    else:
+        assert not torch.equal(got, full)  # the optimistic result was kept
+    # the next call starts from a flag that is down
+    b2 = torch.randn(R, J, K, generator=torch.Generator().manual_seed(2))
+    got2 = tb.lm2exp(ad, b2.cuda(), precision=precision, variant=300000 + tile)
+    tb.check_status()
+    _assert_close(got2.cpu(), a, b2, precision)
+
+
+def test_optimistic_fused_max_pass_is_automatic_for_long_tf32_launches():
+    """cfg3's shape: plain TF32 takes the optimistic max pass, 3xTF32 and short or small problems the full one."""
+    from triturus_b200 import _native
+
+    L = _native.LIB
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 0, 0) == 301282
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 1, 0) == 201282
+    assert L.triturus_b200_lm2exp_plan(4, 256, 256, 256, 0, 0) == 201281  # cfg1: less than one wave
+    assert L.triturus_b200_lm2exp_plan(128, 256, 64, 8192, 0, 0) // 100000 == 2  # two k-blocks: nothing to save
+    assert L.triturus_b200_lm2exp_launches(128, 256, 256, 8192, 0, 0) == 3
+    assert L.triturus_b200_lm2exp_chain_launches(128, 256, 256, 8192, 0, 300000, 1, 0) < 0  # stabiliser supplied
+
+
 def test_tmem_operand_pair_kernel_unaligned_result():
     """K not a multiple of 4: the wrapper pads b, the result rows are not 16-byte aligned and are written row by row."""
     g = torch.Generator().manual_seed(99)

@@ -114,6 +114,17 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ x
   if (lane == 0) m[static_cast<int64_t>(r) * K + k] = clamp_stab(mx);
 }
 
+// Between an optimistic single-CTA launch and the conditional exact launch behind it: moves the flag the first
+// one may have raised into the word the second one reads, and puts the flag down for the next call.
+__global__ void republish_flag_kernel(int* flag) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    flag[1] = flag[0] != 0 ? 1 : 0;
+    flag[0] = 0;
+  }
+}
+
 // Fills m[0..n) with -inf: the start value of the column maxima that an epilogue folds into it.
 __global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* __restrict__ m, int64_t n) {
   for (int64_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) m[i] = -INFINITY;
@@ -385,6 +396,7 @@ struct Lm2expPlan {
   bool tspair;  // ... by the kernel that keeps the generated operand in tensor memory (variants 2566, 2567)
   bool optimistic;  // ... without a pre-pass: stabiliser from the first k-block, exact passes as conditional launches (2567)
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
+  bool optimistic_fused;  // ... over the first k-block of each slab only, exact pass as a conditional launch
   bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
   bool promote_tf32;      // plain TF32 over more than kLongContraction terms: accumulator re-summed in chunks
 };
@@ -398,9 +410,10 @@ constexpr int64_t kLongContraction = 32768;
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
                        bool have_m = false, bool b_km = false) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
-  const int stab_mode = variant / 100000;  // 0 = automatic, 1 = pre-pass, 2 = fused max pass
+  // 0 = automatic, 1 = pre-pass, 2 = fused max pass, 3 = fused max pass over the first k-block only (optimistic)
+  const int stab_mode = variant / 100000;
   int tile_variant = variant % 100000;
-  if (stab_mode > 2 || (have_m && stab_mode == 2)) return TRITURUS_B200_EINVAL;
+  if (stab_mode > 3 || (have_m && stab_mode >= 2)) return TRITURUS_B200_EINVAL;
   if (tile_variant == 0) {
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
@@ -409,14 +422,14 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
-    const bool want_pair = !b_km && stab_mode != 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
+    const bool want_pair = !b_km && stab_mode < 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
     const int pair_variant = precision == TRITURUS_B200_PRECISION_TF32 ? (stab_mode == 0 && !have_m ? 2567 : 2566) : 2564;
     tile_variant = want_pair ? pair_variant : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
-  if (b_km && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567 || stab_mode == 2))
+  if (b_km && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567 || stab_mode >= 2))
     return TRITURUS_B200_EINVAL;
   const bool optimistic = tile_variant == 2567 && stab_mode == 0 && !have_m;
   const bool tspair = tile_variant == 2566 || tile_variant == 2567;
@@ -428,13 +441,13 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   const int mt = tile_variant % 10;
   const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
   if (!pair && ((bn != 128 && bn != 256) || (mt != 1 && mt != 2))) return TRITURUS_B200_EINVAL;
-  if (pair && stab_mode == 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
+  if (pair && stab_mode >= 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
   if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
   // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.  Also when
   // the whole problem is less than one wave of tiles: a second launch then costs more than the row tiles of a
   // slab each scanning it (cfg1: 18.5 us against 21.7 us).
   const bool one_wave = tile_count(R, I, K, bn, mt) <= sm_count();
-  const bool fused = !pair && !b_km && (stab_mode == 2 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
+  const bool fused = !pair && !b_km && (stab_mode >= 2 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
   // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
   // double-buffered so that the epilogue overlaps the next tile.
   if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
@@ -444,6 +457,13 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   out->tspair = tspair;
   out->optimistic = optimistic;
   out->fused = fused && !have_m;
+  // Automatic: where the max pass is a real share of the work (four k-blocks or more) and the launch is long
+  // enough (more than one wave of tiles) for two more, empty, launches not to matter.
+  // Plain TF32 only: in 3xTF32 the shapes concerned are bound by the three MMAs per k-step, not by the max pass
+  // (cfg3: 1.35 ms with, 1.32 ms without).
+  out->optimistic_fused =
+      out->fused && (stab_mode == 3 || (stab_mode == 0 && precision == TRITURUS_B200_PRECISION_TF32 && J >= 128 &&
+                                        tile_count(R, I, K, bn, mt) > sm_count()));
   out->colmax_exclusive = !pair && I <= 128 * mt;
   out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
   return TRITURUS_B200_OK;
@@ -528,7 +548,7 @@ int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, in
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
   // optimistic stabiliser: the contraction and the two conditional launches of the exact passes
-  return plan.fused ? 1 : (plan.optimistic ? 3 : 2);
+  return plan.fused ? (plan.optimistic_fused ? 3 : 1) : (plan.optimistic ? 3 : 2);
 }
 
 int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
@@ -538,7 +558,8 @@ int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int pr
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
-  return (plan.fused ? 2 : (plan.optimistic ? 0 : 1)) * 100000 + plan.bn * 10 + (plan.tspair ? (plan.optimistic ? 7 : 6) : plan.mt);
+  return (plan.fused ? (plan.optimistic_fused ? 3 : 2) : (plan.optimistic ? 0 : 1)) * 100000 + plan.bn * 10 +
+         (plan.tspair ? (plan.optimistic ? 7 : 6) : plan.mt);
 }
 
 // Workspace layout: [two flag words of the optimistic stabiliser, padded to 256 bytes][R x K stabilisers].
@@ -730,14 +751,35 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st, dep)
                                                         : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st, dep);
   }
-  if (precision == TRITURUS_B200_PRECISION_3XTF32) {
-    return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmX_128_1>(ta, tb, to, p, st, dep);
+  auto single = [&](const Lm2expParams& q, bool dependent) -> int {
+    if (precision == TRITURUS_B200_PRECISION_3XTF32) {
+      return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, q, st, dependent)
+                     : launch_lm2exp<LmX_128_1>(ta, tb, to, q, st, dependent);
+    }
+    if (bn == 256)
+      return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, q, st, dependent)
+                     : launch_lm2exp<LmT_256_1>(ta, tb, to, q, st, dependent);
+    if (plan.promote_tf32)
+      return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, q, st, dependent)
+                     : launch_lm2exp<LmP_128_1>(ta, tb, to, q, st, dependent);
+    return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, q, st, dependent)
+                   : launch_lm2exp<LmT_128_1>(ta, tb, to, q, st, dependent);
+  };
+  if (fused && plan.optimistic_fused && ws_flags && out_colmax == nullptr) {
+    // The max pass scans only the first k-block of each slab; a launch that saw a result overflow raises the
+    // flag, one thread moves it to the second word, and the same kernel with the full max pass follows as a
+    // launch that returns at once unless that word is up.
+    int* flag = static_cast<int*>(workspace);
+    Lm2expParams po = p;
+    po.opt_flag = flag;
+    rc = single(po, false);
+    if (rc != TRITURUS_B200_OK) return rc;
+    rc = launch_maybe_dependent(republish_flag_kernel, dim3(1), 32, 0, st, true, flag);
+    if (rc != TRITURUS_B200_OK) return rc;
+    p.only_if = flag + 1;
+    return single(p, true);
   }
-  if (bn == 256)
-    return mt == 2 ? launch_lm2exp<LmT_256_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmT_256_1>(ta, tb, to, p, st, dep);
-  if (plan.promote_tf32)
-    return mt == 2 ? launch_lm2exp<LmP_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmP_128_1>(ta, tb, to, p, st, dep);
-  return mt == 2 ? launch_lm2exp<LmT_128_2>(ta, tb, to, p, st, dep) : launch_lm2exp<LmT_128_1>(ta, tb, to, p, st, dep);
+  return single(p, dep);
 }
 
 // Batches of more than 65535 entries (the limit of gridDim.y / .z in the small kernels) run block by block on
@@ -850,7 +892,7 @@ int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan, have_b_colmax != 0);
   if (rc != TRITURUS_B200_OK) return rc;
-  if (plan.optimistic && !want_out_colmax) return 3;  // as triturus_b200_lm2exp_launches
+  if ((plan.optimistic || plan.optimistic_fused) && !want_out_colmax) return 3;  // as triturus_b200_lm2exp_launches
   return 1 + ((plan.fused || have_b_colmax) ? 0 : 1) + ((want_out_colmax && !plan.colmax_exclusive) ? 1 : 0);
 }
 

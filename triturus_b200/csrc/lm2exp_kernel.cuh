@@ -47,9 +47,9 @@ struct Lm2expParams {
   int b_km = 0;             // b is stored with j contiguous (a transposed view): K-major B operand, one 32 j x BN k
                             // box per stage in the 128-byte swizzle, exp'd in place row by row; pre-pass stabiliser only
   int* status;
-  // Only the TMEM-operand pair kernel reads these two.
+  // The optimistic stabilisers (TMEM-operand pair kernel; fused max pass of the single-CTA kernel):
   const int* only_if = nullptr;  // a conditional launch: the kernel returns at once when *only_if == 0
-  int* opt_flag = nullptr;       // optimistic-stabiliser instances set *opt_flag = 1 when a result overflowed
+  int* opt_flag = nullptr;       // optimistic launches set *opt_flag = 1 when a result overflowed
   int* reset_flag = nullptr;     // a conditional launch that does run puts this word (the flag behind only_if) down
 };
 
@@ -104,6 +104,13 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               const __grid_constant__ CUtensorMap tmap_out, const Lm2expParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS;
   constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP, RP = Cfg::RP;
+
+  // A conditional launch: runs only if the launch before it left the word up (same value for every thread,
+  // read before any barrier or allocation exists).
+  if (p.only_if != nullptr) {
+    pdl_wait();
+    if (*p.only_if == 0) return;
+  }
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128B-swizzled tiles.
@@ -174,6 +181,11 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   const int KB = (p.J + BK - 1) / BK;  // k-blocks per pass
   const bool fused = p.fused_max != 0;
+  // Optimistic fused max pass: only the first k-block of a tile's slab is scanned for the stabiliser; values
+  // further down may exceed it (exp(b - m) > 1, which fp32 holds up to e^88), and a result that overflowed all
+  // the same raises *opt_flag, upon which the caller's conditional launch redoes the call with the full pass.
+  const bool opt = fused && p.opt_flag != nullptr;
+  const int KBM = opt ? 1 : KB;  // k-blocks of the max pass
   // Accumulation chunks per tile and the accumulator buffers they rotate through (see Lm2expCfg::PROMOTE).
   const bool promote = Cfg::PROMOTE && KB > Cfg::CHUNK;
   const int nch = promote ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
@@ -205,7 +217,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const bool prefetch_next = fused && tile + static_cast<int>(gridDim.x) < p.num_tiles;
         if (prefetch_next) decode(tile + gridDim.x, nr, nn0, ni0);
         for (int pass = fused ? 0 : 1; ok && pass < 2; ++pass) {  // 0 = max pass (b only), 1 = contraction
-          for (int kb = 0; kb < KB; ++kb, ++it) {
+          for (int kb = 0; kb < (pass ? KB : KBM); ++kb, ++it) {
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
@@ -251,7 +263,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         if (fused) {
           // Max-pass stages carry no MMA work: hand them back as soon as the transform warps are done.
-          for (int kb = 0; kb < KB; ++kb, ++it) {
+          for (int kb = 0; kb < KBM; ++kb, ++it) {
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
@@ -315,6 +327,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint32_t tcount = 0, ccount = 0;
     uint32_t nblk = 0;  // staging boxes handed to the fold warp so far
     bool ok = true;
+    bool overflowed = false;  // optimistic max pass: some result of this lane came out +inf or NaN
     const bool emit_max = p.out_max != nullptr;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
@@ -407,6 +420,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 o[g * 4 + 3] = m4.w + (PREC ? logf(a3) : lg2_approx(a3) * LN2_F);
               }
             }
+            if (opt) {
+#pragma unroll
+              for (int x = 0; x < 32; ++x) overflowed |= !(o[x] < INFINITY);  // +inf or NaN
+            }
             // Row `lane` of the 32 x 32 block goes to this warp's staging box in the 128-byte swizzle
             // (16-byte chunk g at position g ^ (row % 8): conflict-free).
             // the fold warp (column maxima of the result) has read the previous box
@@ -456,6 +473,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       if (lane == 0) mbar_arrive(&msum_empty[slot]);
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
+    if (opt && __any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
   } else if (warp >= 2 && warp < 4 && p.out_max != nullptr) {
     // ------------------------------------------------------------------ fold: column maxima of the result
     // Warp 2 serves epilogue warps 4 and 5, warp 3 serves 6 and 7: it reads each staged 32 x 32 block of
@@ -512,7 +530,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       if (fused) {
         // ---- max pass: running maximum of this thread's 4 columns over its row slots
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        for (int kb = 0; kb < KBM; ++kb, ++it) {
           const int s = it % NS;
           const uint32_t ph = (it / NS) & 1;
           if (!(ok = mbar_wait_warp(&full[s], ph, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
