@@ -5,10 +5,14 @@
  * All tensor pointers are DEVICE pointers to fp32 data on the device that is current when the call is
  * made.  Strides are in elements.  The innermost stride of every tensor must be 1, every other stride a
  * multiple of 4 elements and every base pointer 16-byte aligned (TMA rules); callers that cannot meet this
- * make a padded copy first (the Python wrappers do).  Exception: the operands a and b of lm2exp may also be
- * transposed views (a with i contiguous, b with j contiguous; the stride-1 dimension swapped, the other rules
- * unchanged), which the kernels read in place; a b of that kind runs on the single-CTA tiles with the pre-pass
- * stabiliser, and variant codes asking for a pair tile or the fused max pass are refused for it.  The library
+ * make a padded copy first (the Python wrappers do).  Exception: the operands a and b of lm2exp may have any
+ * strides (zero and negative ones included; the reference forwards whatever it is given,
+ * triturus/lm2exp.py:190-198).  Transposed views that otherwise meet the rules (a with i contiguous, b with j
+ * contiguous) are read in place through tensor maps, a b of that kind on the single-CTA tiles with the pre-pass
+ * stabiliser.  Any other operand that breaks the rules is fetched element by element by the single-CTA kernel
+ * (about three times slower per k-block than through TMA: for large problems a padded copy is the faster
+ * choice).  Variant codes that ask for a pair tile (or, for a transposed b, the fused max pass) are refused for
+ * such operands, and so are returned column maxima together with an element-wise operand.  The library
  * allocates nothing: the output, the
  * workspace and the status word belong to the caller.  Calls are asynchronous on `stream` and never
  * synchronise; they are re-entrant and may run concurrently on different streams or devices as long as

@@ -52,6 +52,8 @@ def test_argument_validation_returns_codes_without_a_gpu():
     s3 = _native._i64([12, 4, 1])
     null = ctypes.c_void_p(0)
     fake = ctypes.c_void_p(4096)
+    fake2 = ctypes.c_void_p(8192)
+    chain = lib.triturus_b200_lm2exp_chain_f32
     rc = lib.triturus_b200_lm2exp_f32(null, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, 1 << 20, null, null)
     assert rc == -1  # NULL operand
     rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 0, 4, 4, s3, s3, s3, 0, 0, fake, 1 << 20, null, null)
@@ -60,12 +62,17 @@ def test_argument_validation_returns_codes_without_a_gpu():
     assert rc == -1  # unknown precision
     rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, 8, null, null)
     assert rc == -3  # workspace too small
+    # (operands a and b may have any strides; the result must have innermost stride 1, and fp32 data is 4-byte aligned)
     bad = _native._i64([12, 4, 2])
-    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, bad, s3, s3, 0, 0, fake, 1 << 20, null, null)
-    assert rc == -2  # innermost stride must be 1
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 1, 1, 4, 4, s3, s3, bad, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -2  # innermost stride of the result must be 1
+    rc = lib.triturus_b200_lm2exp_f32(ctypes.c_void_p(4098), fake, fake, 1, 1, 4, 4, s3, s3, s3, 0, 0, fake, 1 << 20, null, null)
+    assert rc == -2  # operand not 4-byte aligned
     odd = _native._i64([14, 7, 1])
-    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 2, 2, 4, 4, odd, s3, s3, 0, 0, fake, 1 << 20, null, null)
-    assert rc == -2  # row stride not a multiple of 4 elements
+    rc = lib.triturus_b200_lm2exp_f32(fake, fake, fake, 2, 2, 4, 4, odd, s3, s3, 0, 2564, fake, 1 << 20, null, null)
+    assert rc == -1  # a row stride that is not a multiple of 4 elements cannot go with a pair tile
+    rc = chain(fake, fake, fake, 2, 2, 4, 4, odd, s3, s3, 0, 0, fake, fake2, fake, 1 << 20, null, null)
+    assert rc == -2  # ... nor with returned column maxima
     s4 = _native._i64([48, 16, 4, 1])
     rc = lib.triturus_b200_lt2exp_f32(fake, fake, fake, null, 1, 1, 4, 4, 4, s4, s3, s3, s3, 0, 0, null, null)
     assert rc == -1

@@ -520,6 +520,79 @@ def test_transposed_b_special_cases():
     assert rc == -1, rc  # TRITURUS_B200_EINVAL
 
 
+def _raw_lm2exp(a, b, precision, variant=0):
+    """The C ABI called on the tensors as they are (no wrapper in between that could copy)."""
+    from triturus_b200 import _native
+
+    R, I, J = a.shape
+    K = b.shape[2]
+    out = torch.empty(R, I, K, device="cuda")
+    nbytes = int(_native.LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
+    ws = torch.zeros(nbytes // 4 + 64, device="cuda")
+    rc = _native.LIB.triturus_b200_lm2exp_f32(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), R, I, J, K, _native._i64(a.stride()), _native._i64(b.stride()),
+        _native._i64(out.stride()), 0 if precision == "tf32" else 1, variant, ws.data_ptr(), nbytes,
+        _native._status_word(a.device).data_ptr(), None)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+@pytest.mark.parametrize("variant", [0, 1281, 1282, 2561, 101282, 201281, 301281])
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("shape", [(2, 130, 101, 263), (1, 64, 33, 5), (3, 257, 250, 517), (2, 100, 7, 1030),
+                                   (1, 300, 1026, 130)])
+def test_operands_that_break_the_tensor_map_rules_are_read_in_place(shape, precision, variant):
+    """Odd extents everywhere (rows of a and b that do not start on 16-byte boundaries; the reference forwards any
+    strides, triturus/lm2exp.py:190-198): the C ABI takes the tensors as they are and the single-CTA kernel
+    fetches them element by element.  Several tiles per CTA, partial tiles on every edge, -inf entries and an all
+    -inf column; pre-pass, fused and optimistic max pass."""
+    import triturus_b200 as tb
+
+    if precision == "3xtf32" and variant % 100000 == 2561:
+        pytest.skip("3xTF32 tiles have 128 columns")
+    R, I, J, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + variant)
+    a = torch.rand(R, I, J, generator=g)
+    b = torch.randn(R, J, K, generator=g) * 6.0 + 50.0 * torch.randn(R, 1, K, generator=g)
+    b[0, :, min(3, K - 1)] = float("-inf")
+    b[torch.rand(R, J, K, generator=g) < 0.01] = float("-inf")
+    rc, got = _raw_lm2exp(a.cuda(), b.cuda(), precision, variant)
+    assert rc == 0, rc
+    tb.check_status()
+    assert torch.all(got[0, :, min(3, K - 1)] == float("-inf"))
+    _assert_close(got.cpu(), a, b, precision)
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_strided_and_broadcast_views_in_place(precision):
+    """Every third row and every second column of a, every second column of b, a b broadcast over the batch
+    (stride 0) and a base that is only 4-byte aligned: through the wrapper, which for problems of this size makes
+    no copy, and through the C ABI; a pair tile asked for with such operands is refused by the C ABI."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    g = torch.Generator().manual_seed(21)
+    a_full = torch.rand(2, 3 * 70, 2 * 48 + 1, generator=g).cuda()
+    b_full = (torch.randn(2, 48, 2 * 200 + 2, generator=g) * 4.0).cuda()
+    a_v, b_v = a_full[:, ::3, 1::2], b_full[:, :, 1::2][:, :, :200]
+    flop = 2.0 * 2 * 70 * 48 * 200
+    assert _native._in_place_small(a_v, flop, 0, False)
+    assert _native._lm2exp_b_operand(b_v, 0, flop).data_ptr() == b_v.data_ptr()
+    got = tb.lm2exp(a_v, b_v, precision=precision)
+    tb.check_status()
+    _assert_close(got.cpu(), a_v.cpu().contiguous(), b_v.cpu().contiguous(), precision)
+    b_b = (torch.randn(1, 48, 200, generator=g) * 3.0).cuda().expand(2, 48, 200)
+    rc, got = _raw_lm2exp(a_v, b_b, precision)
+    assert rc == 0
+    tb.check_status()
+    _assert_close(got.cpu(), a_v.cpu().contiguous(), b_b.cpu().contiguous(), precision)
+    rc, _ = _raw_lm2exp(a_v, b_v, "tf32", 2564)
+    assert rc == -1  # TRITURUS_B200_EINVAL
+    # a large problem with an odd extent still gets the padded copy from the wrapper (faster there)
+    big = torch.rand(32, 1024, 1022, device="cuda")
+    assert not _native._in_place_small(big, 2.0 * 32 * 1024 * 1022 * 1024, 0, False)
+
+
 def test_batches_beyond_the_grid_limit():
     """More than 65535 batch entries (the reference's 1-D grid takes any batch, triturus/lm2exp.py:177-181): the
     library runs them in blocks of 65535 on the same stream."""

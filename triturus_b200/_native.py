@@ -213,16 +213,17 @@ def check_status(device=None) -> None:
         raise NativeLibraryError(f"device-side failure {code}: {strerror(code)}")
 
 
+def _tma_ok(t: torch.Tensor) -> bool:
+    """Innermost stride 1, other strides positive multiples of 4 elements, base 16-byte aligned: what a TMA
+    tensor map needs."""
+    if t.data_ptr() % 16 != 0 or not (t.shape[-1] == 1 or t.stride(-1) == 1):
+        return False
+    return all(t.shape[d] == 1 or (t.stride(d) > 0 and t.stride(d) % 4 == 0) for d in range(t.dim() - 1))
+
+
 def _tma_ready(t: torch.Tensor) -> torch.Tensor:
-    """Return `t` or a padded copy whose innermost stride is 1, other strides multiples of 4 elements and
-    base 16-byte aligned (what a TMA tensor map needs).  The logical shape is unchanged."""
-    ok = t.data_ptr() % 16 == 0 and (t.shape[-1] == 1 or t.stride(-1) == 1)
-    if ok:
-        for d in range(t.dim() - 1):
-            if t.shape[d] > 1 and (t.stride(d) <= 0 or t.stride(d) % 4 != 0):
-                ok = False
-                break
-    if ok:
+    """Return `t` or a padded copy that meets `_tma_ok`.  The logical shape is unchanged."""
+    if _tma_ok(t):
         return t
     inner = t.shape[-1]
     padded = (inner + 3) // 4 * 4
@@ -230,6 +231,20 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     view = buf[..., :inner]
     view.copy_(t)
     return view
+
+
+# Problems up to this many FLOP take operands that break the tensor-map rules in place (the single-CTA kernel then
+# fetches them element by element, ~3x slower per k-block than through TMA); larger ones get the padded copy, which
+# is the cheaper of the two there.  Measured: R24 150x101x203 0.035 ms in place / 0.072 ms with the copy;
+# R32 1024x1024x1022 0.75 / 0.26 ms; R128 256x256x8190 1.20 / 1.60 ms in TF32 but 2.97 / 2.32 ms in 3xTF32.
+_IN_PLACE_MAX_FLOP = 8e9
+
+
+def _in_place_small(t: torch.Tensor, flop: float, variant: int, want_colmax: bool) -> bool:
+    """True when `t` should go to the library as it is although a tensor map cannot describe it."""
+    tile = int(variant) % 100000
+    return (flop <= _IN_PLACE_MAX_FLOP and not want_colmax and tile in _SINGLE_CTA_TILES
+            and t.dtype == torch.float32 and t.data_ptr() % 4 == 0)
 
 
 def _lm2exp_a_operand(a: torch.Tensor, K: int) -> torch.Tensor:
@@ -250,16 +265,24 @@ def _lm2exp_a_operand(a: torch.Tensor, K: int) -> torch.Tensor:
     return _tma_ready(a)
 
 
-def _lm2exp_b_operand(b: torch.Tensor, variant: int) -> torch.Tensor:
-    """b as the kernel takes it.  A transposed view (j contiguous, e.g. `x.transpose(1, 2)` of a contiguous x)
-    that meets the tensor-map rules is read in place as a K-major operand by the single-CTA kernel, with the
-    pre-pass stabiliser; variant codes that ask for a pair tile or the fused max pass get a copy instead."""
+_SINGLE_CTA_TILES = (0, 1281, 1282, 2561, 2562)
+
+
+def _lm2exp_b_operand(b: torch.Tensor, variant: int, flop: float = float("inf"), want_colmax: bool = False) -> torch.Tensor:
+    """b as the kernel takes it.  Unchanged when the TMA rules hold.  A transposed view (j contiguous, e.g.
+    `x.transpose(1, 2)` of a contiguous x) that meets them otherwise is read in place as a K-major operand by the
+    single-CTA kernel, with the pre-pass stabiliser; variant codes that ask for a pair tile or the fused max pass
+    get a copy instead.  Anything else goes in place when the problem is small (`_in_place_small`), else as a
+    padded copy."""
     R, J, K = b.shape
     tile, stab = int(variant) % 100000, int(variant) // 100000
+    if _tma_ok(b):
+        return b
     if K > 1 and b.stride(2) != 1 and (J == 1 or b.stride(1) == 1) and b.data_ptr() % 16 == 0:
-        ok = b.stride(2) > 0 and b.stride(2) % 4 == 0 and (R == 1 or (b.stride(0) > 0 and b.stride(0) % 4 == 0))
-        if ok and tile in (0, 1281, 1282, 2561, 2562) and stab != 2:
-            return b
+        if b.stride(2) > 0 and b.stride(2) % 4 == 0 and (R == 1 or (b.stride(0) > 0 and b.stride(0) % 4 == 0)):
+            return b if (tile in _SINGLE_CTA_TILES and stab < 2) else _tma_ready(b)
+    if _in_place_small(b, flop, variant, want_colmax):
+        return b
     return _tma_ready(b)
 
 
@@ -313,8 +336,9 @@ def _lm2exp_impl(a: torch.Tensor, b: torch.Tensor, precision: int, variant: int)
     _require_cuda(a, b)
     R, I, J = a.shape
     K = b.shape[2]
-    a = _lm2exp_a_operand(a, K)
-    b = _lm2exp_b_operand(b, variant)
+    flop = 2.0 * R * I * J * K
+    a = a if _in_place_small(a, flop, variant, False) else _lm2exp_a_operand(a, K)
+    b = _lm2exp_b_operand(b, variant, flop, False)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     ws_bytes = int(LIB.triturus_b200_lm2exp_workspace_bytes(R, I, J, K))
     with _on_device(a.device) as idx:
@@ -337,8 +361,9 @@ def _lm2exp_chain_impl(
     _require_cuda(a, b)
     R, I, J = a.shape
     K = b.shape[2]
-    a = _lm2exp_a_operand(a, K)
-    b = _lm2exp_b_operand(b, variant)
+    flop = 2.0 * R * I * J * K
+    a = a if _in_place_small(a, flop, variant, want_colmax) else _lm2exp_a_operand(a, K)
+    b = _lm2exp_b_operand(b, variant, flop, want_colmax)
     out = torch.empty((R, I, K), dtype=torch.float32, device=a.device)
     out_colmax = torch.empty((R, K) if want_colmax else (0,), dtype=torch.float32, device=a.device)
     if b_colmax is not None:

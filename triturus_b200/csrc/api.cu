@@ -25,7 +25,8 @@ namespace tb200 {
 // folds the four row slots with warp shuffles.
 template <bool VEC>
 __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
-                                                      int64_t s0, int64_t s1, const int* only_if, int* publish) {
+                                                      int64_t s0, int64_t s1, int64_t s2, const int* only_if,
+                                                      int* publish) {
   __shared__ float part[8][32];
   // The contraction kernel that consumes m may be launched as a programmatic dependent: let it start its set-up
   // (barriers, tensor memory, first operand tiles) as soon as every block of this grid is running.
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
     const int c = c0 + lane;
     float mx = -INFINITY;
     if (c < K) {
-      for (int j = warp; j < J; j += 8) mx = fmaxf(mx, __ldg(xb + static_cast<int64_t>(j) * s1 + c));
+      for (int j = warp; j < J; j += 8) mx = fmaxf(mx, __ldg(xb + static_cast<int64_t>(j) * s1 + c * s2));
     }
     part[warp][lane] = mx;
   }
@@ -407,8 +408,9 @@ constexpr int64_t kLongContraction = 32768;
 
 // have_m: the caller supplies the stabiliser, so the tile is chosen as usual but no max pass of either kind runs.
 // b_km: b is stored with j contiguous; only the single-CTA kernel takes it, with the pre-pass stabiliser.
+// single_cta: an operand is fetched element by element, which only the single-CTA kernel does.
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
-                       bool have_m = false, bool b_km = false) {
+                       bool have_m = false, bool b_km = false, bool single_cta = false) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
   // 0 = automatic, 1 = pre-pass, 2 = fused max pass, 3 = fused max pass over the first k-block only (optimistic)
   const int stab_mode = variant / 100000;
@@ -422,7 +424,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
-    const bool want_pair = !b_km && stab_mode < 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
+    const bool want_pair = !b_km && !single_cta && stab_mode < 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
@@ -431,6 +433,7 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   }
   if (b_km && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567 || stab_mode >= 2))
     return TRITURUS_B200_EINVAL;
+  if (single_cta && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567)) return TRITURUS_B200_EINVAL;
   const bool optimistic = tile_variant == 2567 && stab_mode == 0 && !have_m;
   const bool tspair = tile_variant == 2566 || tile_variant == 2567;
   if (tspair) {
@@ -522,17 +525,17 @@ static int colmax_run(const float* x, float* m, int64_t R, int64_t J, int64_t K,
     }
     return TRITURUS_B200_OK;
   }
-  if (K > 1 && x_strides[2] != 1) return TRITURUS_B200_EALIGN;
-  const bool vec = (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
+  const int64_t s2 = K > 1 ? x_strides[2] : 1;
+  const bool vec = s2 == 1 && (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
   const dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(R));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // (a conditional launch follows the optimistic contraction as its programmatic dependent)
   const bool dep = only_if != nullptr;
   const int Ji = static_cast<int>(J), Ki = static_cast<int>(K);
   return vec ? launch_maybe_dependent(colmax_kernel<true>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
-                                      only_if, publish)
+                                      s2, only_if, publish)
              : launch_maybe_dependent(colmax_kernel<false>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
-                                      only_if, publish);
+                                      s2, only_if, publish);
 }
 
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
@@ -596,33 +599,40 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
   int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
   int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
-  // b with k contiguous is an MN-major tensor-core operand; a transposed view (j contiguous) is used in place as
-  // a K-major operand by the single-CTA kernel.
-  const bool b_km = K > 1 && bs2 != 1;
-  if (b_km && J > 1 && bs1 != 1) return TRITURUS_B200_EALIGN;
   if (K > 1 && os2 != 1) return TRITURUS_B200_EALIGN;
-  if (!aligned16(a) || !aligned16(b)) return TRITURUS_B200_EALIGN;
-  // a with j contiguous is a K-major tensor-core operand; a transposed view (i contiguous) is used in place
-  // as an MN-major operand.
-  const bool a_mn = J > 1 && as2 != 1;
-  if (a_mn) {
-    if (I > 1 && as1 != 1) return TRITURUS_B200_EALIGN;
-    if (!fix_stride(J, as2, round_up4(I)) || !fix_stride(R, as0, round_up4(I) * J)) return TRITURUS_B200_EALIGN;
-  } else if (!fix_stride(I, as1, round_up4(J)) || !fix_stride(R, as0, round_up4(J) * I)) {
-    return TRITURUS_B200_EALIGN;
-  }
-  if (b_km) {
-    if (!fix_stride(K, bs2, round_up4(J)) || !fix_stride(R, bs0, round_up4(J) * K)) return TRITURUS_B200_EALIGN;
-  } else if (!fix_stride(J, bs1, round_up4(K)) || !fix_stride(R, bs0, round_up4(K) * J)) {
-    return TRITURUS_B200_EALIGN;
-  }
   if (I > 1 && os1 <= 0) return TRITURUS_B200_EALIGN;
   if (R > 1 && os0 <= 0) return TRITURUS_B200_EALIGN;
+  if ((reinterpret_cast<uintptr_t>(a) & 3) != 0 || (reinterpret_cast<uintptr_t>(b) & 3) != 0) return TRITURUS_B200_EALIGN;
+  // How each operand reaches shared memory.  a with j contiguous is a K-major tensor-core operand, a transposed
+  // view (i contiguous) an MN-major one; b with k contiguous is MN-major, a transposed view (j contiguous)
+  // K-major (single-CTA kernel only).  All four go through tensor maps when base and strides meet the TMA rules;
+  // an operand that does not (row pitch not a multiple of 16 bytes, innermost stride other than 1, base not
+  // 16-byte aligned) is fetched element by element by the single-CTA kernel instead (gen_a / gen_b).
+  const int64_t as_raw[3] = {as0, as1, as2}, bs_raw[3] = {bs0, bs1, bs2};
+  bool a_mn = J > 1 && as2 != 1;
+  bool a_tma = aligned16(a);
+  if (a_tma && a_mn) {
+    a_tma = (I == 1 || as1 == 1) && fix_stride(J, as2, round_up4(I)) && fix_stride(R, as0, round_up4(I) * J);
+  } else if (a_tma) {
+    a_tma = fix_stride(I, as1, round_up4(J)) && fix_stride(R, as0, round_up4(J) * I);
+  }
+  bool b_km = K > 1 && bs2 != 1;
+  bool b_tma = aligned16(b);
+  if (b_tma && b_km) {
+    b_tma = (J == 1 || bs1 == 1) && fix_stride(K, bs2, round_up4(J)) && fix_stride(R, bs0, round_up4(J) * K);
+  } else if (b_tma) {
+    b_tma = fix_stride(J, bs1, round_up4(K)) && fix_stride(R, bs0, round_up4(K) * J);
+  }
+  const bool gen_a = !a_tma, gen_b = !b_tma;
+  if (gen_a) a_mn = false;
+  if (gen_b) b_km = false;
+  // (the element-wise loader takes the place of the warps that fold the column maxima of the result)
+  if ((gen_a || gen_b) && out_colmax != nullptr) return TRITURUS_B200_EALIGN;
 
   Lm2expPlan plan;
   {
     // A supplied stabiliser makes every max pass redundant (and a fused max pass cannot be requested as well).
-    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan, b_colmax != nullptr, b_km);
+    const int prc = plan_lm2exp(R, I, J, K, precision, variant, &plan, b_colmax != nullptr, b_km, gen_a || gen_b);
     if (prc != TRITURUS_B200_OK) return prc;
   }
   const int bn = plan.bn, mt = plan.mt;
@@ -647,7 +657,11 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   const bool prepass = !fused && b_colmax == nullptr;
 
   CUtensorMap ta, tb;
-  if (a_mn) {
+  memset(&ta, 0, sizeof(ta));
+  memset(&tb, 0, sizeof(tb));
+  if (gen_a) {
+    // (no tensor map)
+  } else if (a_mn) {
     const int64_t dims[3] = {I, J, R};
     const int64_t strides[3] = {1, as2, as0};
     const uint32_t box[3] = {32, 32, 1};
@@ -660,7 +674,9 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     rc = make_tmap(&ta, a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TRITURUS_B200_OK) return rc;
   }
-  if (b_km) {
+  if (gen_b) {
+    // (no tensor map)
+  } else if (b_km) {
     const int64_t dims[3] = {J, K, R};
     const int64_t strides[3] = {1, bs2, bs0};
     const uint32_t box[3] = {32, static_cast<uint32_t>(bn), 1};
@@ -692,6 +708,12 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   p.out_tma = out_tma ? 1 : 0;
   p.a_mn = a_mn ? 1 : 0;
   p.b_km = b_km ? 1 : 0;
+  p.gen_a = gen_a ? 1 : 0;
+  p.gen_b = gen_b ? 1 : 0;
+  p.a_ptr = a;
+  p.b_ptr = b;
+  p.a_s0 = as_raw[0], p.a_s1 = as_raw[1], p.a_s2 = as_raw[2];
+  p.b_s0 = bs_raw[0], p.b_s1 = bs_raw[1], p.b_s2 = bs_raw[2];
   p.m_ws = m_ws;
   p.out = out;
   p.out_max = out_colmax;
@@ -717,7 +739,7 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     rc = make_tmap(&tb_plain, b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != TRITURUS_B200_OK) return rc;
   }
-  const int64_t bstr[3] = {bs0, bs1, 1};
+  const int64_t bstr[3] = {gen_b ? bs_raw[0] : bs0, gen_b ? bs_raw[1] : bs1, gen_b ? bs_raw[2] : 1};
   if (use_ts && plan.optimistic && prepass && ws_flags) {
     // No pre-pass: the contraction takes each column's stabiliser from its first 32 rows and raises the flag
     // if a result overflowed; the exact pre-pass and contraction follow as launches that return at once

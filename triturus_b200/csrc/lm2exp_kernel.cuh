@@ -46,6 +46,13 @@ struct Lm2expParams {
                             // four 32 i x 32 j boxes per 128-row tile in the layout of the b boxes
   int b_km = 0;             // b is stored with j contiguous (a transposed view): K-major B operand, one 32 j x BN k
                             // box per stage in the 128-byte swizzle, exp'd in place row by row; pre-pass stabiliser only
+  // Operands that break the tensor-map rules (a row pitch that is not a multiple of 16 bytes, an innermost stride
+  // other than 1, an unaligned base) are fetched element by element with 4-byte asynchronous copies by warps 2-3
+  // into the same swizzled stages; gen_a / gen_b say which, the pointers and element strides are theirs.
+  int gen_a = 0, gen_b = 0;
+  const float* a_ptr = nullptr;
+  const float* b_ptr = nullptr;
+  int64_t a_s0 = 0, a_s1 = 0, a_s2 = 0, b_s0 = 0, b_s1 = 0, b_s2 = 0;
   int* status;
   // The optimistic stabilisers (TMEM-operand pair kernel; fused max pass of the single-CTA kernel):
   const int* only_if = nullptr;  // a conditional launch: the kernel returns at once when *only_if == 0
@@ -149,7 +156,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], 1 + ((p.gen_a || p.gen_b) ? 64 : 0));  // + the 64 threads of the element-wise loader
       mbar_init(&xf_done[s], NTW);
       mbar_init(&stage_empty[s], 1);
     }
@@ -165,8 +172,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&box_free[s], 1);
     }
     fence_mbar_init();
-    tma_prefetch_desc(&tmap_a);
-    tma_prefetch_desc(&tmap_b);
+    if (!p.gen_a) tma_prefetch_desc(&tmap_a);  // (a tensor map that is not used is all zeros)
+    if (!p.gen_b) tma_prefetch_desc(&tmap_b);
     if (p.out_tma) tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
@@ -221,8 +228,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
-            mbar_arrive_expect_tx(&full[s], (pass ? MT * Cfg::A_TILE : 0) + Cfg::B_TILE);
-            if (pass) {
+            mbar_arrive_expect_tx(&full[s], ((pass && !p.gen_a) ? MT * Cfg::A_TILE : 0) + (p.gen_b ? 0 : Cfg::B_TILE));
+            if (pass && !p.gen_a) {
               if (p.a_mn) {
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
@@ -234,12 +241,14 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 #pragma unroll
                 for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
               }
-              if (prefetch_next) {
-#pragma unroll
-                for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
-              }
             }
-            if (p.b_km) {
+            if (pass && prefetch_next && !p.gen_b) {
+#pragma unroll
+              for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
+            }
+            if (p.gen_b) {
+              // (warps 2-3 fetch the b tile)
+            } else if (p.b_km) {
               tma_load_3d(b_tile(s, 0), &tmap_b, &full[s], kb * BK, n0, r);  // rows k of 32 j: the layout of an a tile
             } else {
 #pragma unroll
@@ -474,6 +483,62 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
     if (opt && __any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
+  } else if (warp >= 2 && warp < 4 && (p.gen_a || p.gen_b)) {
+    // ------------------------------------------------------------------ element-wise loader (never with out_max)
+    // Walks the stages exactly as the TMA producer does and fills the tiles of the operands it is responsible
+    // for.  A stage is reported `LAG` stages late: each thread waits for its own copies of that stage
+    // (cp.async groups), makes them visible to the tensor core's proxy and arrives on the stage's barrier.
+    constexpr int LAG = NS > 2 ? 2 : 1;
+    const int lt = threadIdx.x - 64;  // 0..63
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int r, n0, i0;
+      decode(tile, r, n0, i0);
+      const float* ar = p.a_ptr + static_cast<int64_t>(r) * p.a_s0;
+      const float* br = p.b_ptr + static_cast<int64_t>(r) * p.b_s0;
+      for (int pass = fused ? 0 : 1; ok && pass < 2; ++pass) {
+        for (int kb = 0; kb < (pass ? KB : KBM); ++kb, ++it) {
+          const int s = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!(ok = mbar_wait_warp(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
+          const int j0 = kb * BK;
+          if (pass && p.gen_a) {
+            // a tile: 128 x MT rows i of 32 values j, K-major, 128-byte swizzle; consecutive threads consecutive j
+            for (int e = lt; e < MT * BM * BK; e += 64) {
+              const int row = e >> 5, j = e & 31;
+              const int t = row >> 7, rr = row & 127;
+              const bool valid = i0 + row < p.I && j0 + j < p.J;
+              const float* src = ar + static_cast<int64_t>(i0 + row) * p.a_s1 + static_cast<int64_t>(j0 + j) * p.a_s2;
+              cp_async_f32(smem_u32(a_tile(s, 0, t)) + sw128_offset(rr, j), valid ? src : p.a_ptr, valid);
+            }
+          }
+          if (p.gen_b) {
+            // b tile: 32 rows j of BN values k in boxes of 32 columns; consecutive threads consecutive k
+            for (int e = lt; e < BK * BN; e += 64) {
+              const int j = e / BN, k = e % BN;
+              const bool valid = j0 + j < p.J && n0 + k < p.K;
+              const float* src = br + static_cast<int64_t>(j0 + j) * p.b_s1 + static_cast<int64_t>(n0 + k) * p.b_s2;
+              const uint32_t dst = smem_u32(b_tile(s, 0)) + (k >> 5) * Cfg::B_BOX + sw128_base32_offset(j, (k & 31) >> 2) +
+                                   (k & 3) * 4;
+              cp_async_f32(dst, valid ? src : p.b_ptr, valid);
+            }
+          }
+          cp_async_commit();
+          if (it >= LAG) {
+            cp_async_wait<LAG>();
+            fence_proxy_async_smem();
+            mbar_arrive(&full[(it - LAG) % NS]);
+          }
+        }
+      }
+    }
+    // the last LAG stages
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    if (ok) {
+      for (uint32_t d = (it < LAG ? it : LAG); d > 0; --d) mbar_arrive(&full[(it - d) % NS]);
+    }
   } else if (warp >= 2 && warp < 4 && p.out_max != nullptr) {
     // ------------------------------------------------------------------ fold: column maxima of the result
     // Warp 2 serves epilogue warps 4 and 5, warp 3 serves 6 and 7: it reads each staged 32 x 32 block of

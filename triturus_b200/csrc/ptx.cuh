@@ -116,6 +116,19 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, c
   return __all_sync(0xffffffffu, ok);
 }
 
+// ----------------------------------------------------------------------------- 4-byte asynchronous copies
+//
+// For operands that a tensor map cannot describe (rows that do not start on 16-byte boundaries, an innermost
+// stride other than 1): one element per copy, zeros where `valid` is false (the source is then not read).
+__device__ __forceinline__ void cp_async_f32(uint32_t smem_dst, const float* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ----------------------------------------------------------------------------- CTA pairs (clusters of two)
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
