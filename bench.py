@@ -626,14 +626,15 @@ def main() -> None:
     n_launch = launches_per_step(wl, args.precision, args.variant, args.chain)
     kernel_ms = prepass_ms = None
     pcode = plan_code(wl, args.precision, args.variant)
-    stab = pcode // 100000 if wl.op == "lm2exp" else -1  # 0 optimistic pair kernel, 1 pre-pass, 2 / 3 fused max pass
-    if stab in (0, 1) and not args.chain and not args.profile_mode:
+    # 0 optimistic TMEM-operand pair kernel, 1 pre-pass, 2 / 3 fused max pass, 4 optimistic 32-row pre-pass
+    stab = pcode // 100000 if wl.op == "lm2exp" else -1
+    if stab in (0, 1, 4) and not args.chain and not args.profile_mode:
         m_pre = tb.colmax(inputs[1])
         kern = lambda: tb.lm2exp(*inputs, precision=args.precision, variant=args.variant, b_colmax=m_pre)  # noqa: E731
         for _ in range(3):
             kern()
         kernel_ms = statistics.median(time_steps(kern, max(20, min(steps, 100)), flush))
-        if n_launch == 2:  # (3 launches: optimistic stabiliser, no pre-pass in the step)
+        if stab == 1:  # (the optimistic forms have no full pre-pass in the step)
             prepass_ms = statistics.median(time_steps(lambda: tb.colmax(inputs[1]), max(20, min(steps, 100)), flush))
     n_before = len(sampler.lines)
     lead_out_deadline = time.perf_counter() + (0.0 if args.profile_mode else 1.5)
@@ -806,7 +807,9 @@ def main() -> None:
                            "lm2exp_tspair_kernel with the optimistic stabiliser (+ two conditional launches of the exact "
                            "passes, which return at once)" if stab == 0 else
                            "lm2exp_kernel, max pass over the first k-block of each slab (+ flag hand-over and the "
-                           "conditional launch of the full pass, which returns at once)" if stab == 3
+                           "conditional launch of the full pass, which returns at once)" if stab == 3 else
+                           "colmax_kernel over the first 32 rows + lm2exp_pair_kernel (+ two conditional launches of "
+                           "the exact passes, which return at once)" if stab == 4
                            else "lm2exp_kernel (fused max pass)"))
         if kernel_ms is not None:
             dom = roofline_of(wl, kernel_ms, peaks, clocks)

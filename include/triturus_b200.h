@@ -65,7 +65,8 @@ const char* triturus_b200_strerror(int code);
  *              only; 2567 = 2566 with the optimistic stabiliser described below)
  *              and STAB selecting where the stabiliser is computed: 0 = automatic, 1 = pre-pass launch
  *              writing the workspace, 2 = max pass fused into the contraction kernel (not with the pair tiles),
- *              3 = that max pass over the first 32 rows of each slab only (optimistic, see below).
+ *              3 = that max pass over the first 32 rows of each slab only (optimistic, see below),
+ *              4 = pre-pass over the first 32 rows only (optimistic; tile 2564).
  *              (The counterpart of the reference's autotune table, triturus/lm2exp.py:7-58.)
  *   workspace: triturus_b200_lm2exp_workspace_bytes(R, I, J, K) bytes, 256-byte aligned: two flag words padded
  *              to 256 bytes, then the [R,K] stabiliser.  A workspace of only R * K floats is accepted too; the
@@ -83,13 +84,17 @@ const char* triturus_b200_strerror(int code);
  * kernel has the same form for its fused max pass (STAB = 3; automatic for plain TF32 when the contraction has
  * four k-blocks or more and the launch more than one wave of tiles): the pass scans one k-block instead of the
  * whole slab, one thread moves the flag to the second word and puts it down, and the same kernel with the full
- * pass follows as the conditional launch.  Not used when column maxima of the result are requested.  The reference
+ * pass follows as the conditional launch.  The shared-memory pair kernel (tile 2564; the automatic choice in
+ * 3xTF32) has it as STAB = 4: the pre-pass launch scans 32 rows instead of J, then the contraction and the two
+ * conditional launches (4 in all).  None of the three is used when column maxima of the result are requested.
+ * The reference
  * finds the exact maximum in a first loop over j inside its kernel (triturus/lm2exp.py:124-127).
  */
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K);
 /* Number of kernels one triturus_b200_lm2exp_f32 call launches for these arguments on the current device:
- * 2 (stabiliser pre-pass + contraction), 1 (fused max pass) or 3 (optimistic stabiliser of either kernel: the
- * contraction and two more launches that return at once; a with j contiguous and a full-size workspace assumed);
+ * 2 (stabiliser pre-pass + contraction), 1 (fused max pass), 3 or 4 (the optimistic stabilisers: 32-row pre-pass
+ * where the kernel needs one, the contraction, and two more launches that return at once; a with j contiguous and
+ * a full-size workspace assumed);
  * negative on invalid arguments.  The reference
  * has no counterpart (its launch count is Triton's business, triturus/lm2exp.py:186-205). */
 int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);

@@ -133,6 +133,42 @@ def test_optimistic_stabiliser(case):
         tb.lm2exp(ad, bd, precision="3xtf32", variant=2567)
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
+@pytest.mark.parametrize("case", list(_optimistic_cases()), ids=lambda c: c[0])
+def test_optimistic_prepass_of_the_shared_memory_pair_kernel(case, precision):
+    """Stabiliser code 4 (variant 402564; automatic for 3xTF32 on pair tiles): the pre-pass takes the column maxima
+    over the first 32 rows of b only, the pair kernel checks its results for overflow, and the full pre-pass and
+    the contraction with its maxima follow as conditional launches.  Where they ran, the result is bit for bit
+    that of the pre-pass variant 102564."""
+    import triturus_b200 as tb
+    from triturus_b200 import _native
+
+    name, a, b, exact = case
+    R, I, J = a.shape
+    K = b.shape[2]
+    prec = 0 if precision == "tf32" else 1
+    if J < 128:
+        assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, prec, 402564) == 102564  # nothing to save
+        return
+    assert _native.LIB.triturus_b200_lm2exp_plan(R, I, J, K, prec, 402564) == 402564
+    assert _native.LIB.triturus_b200_lm2exp_launches(R, I, J, K, prec, 402564) == 4
+    ad, bd = a.cuda(), b.cuda()
+    got = tb.lm2exp(ad, bd, precision=precision, variant=402564)
+    tb.check_status()
+    _assert_close(got.cpu(), a, b, precision)
+    pre = tb.lm2exp(ad, bd, precision=precision, variant=102564)
+    tb.check_status()
+    assert torch.equal(torch.isinf(got), torch.isinf(pre))
+    if exact:
+        assert torch.equal(got, pre)
+    elif name in ("random", "later-rows-30-above", "later-rows-70-above"):
+        assert not torch.equal(got, pre)  # the optimistic result was kept
+    b2 = torch.randn(R, J, K, generator=torch.Generator().manual_seed(1))
+    got2 = tb.lm2exp(ad, b2.cuda(), precision=precision, variant=402564)
+    tb.check_status()
+    _assert_close(got2.cpu(), a, b2, precision)
+
+
 def test_optimistic_stabiliser_is_the_automatic_choice_for_tf32_pairs():
     """cfg2's shape: plain TF32 runs the optimistic TMEM-operand kernel, 3xTF32 the shared-memory pair kernel with
     the pre-pass; a supplied stabiliser or a forced pre-pass leaves the optimistic form out."""
@@ -140,7 +176,9 @@ def test_optimistic_stabiliser_is_the_automatic_choice_for_tf32_pairs():
 
     L = _native.LIB
     assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 0, 0) == 2567
-    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 1, 0) == 102564
+    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 1, 0) == 402564  # 3xTF32: optimistic 32-row pre-pass
+    assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 1, 2564) == 102564  # an explicit tile keeps the full one
+    assert L.triturus_b200_lm2exp_launches(32, 1024, 1024, 1024, 1, 0) == 4
     assert L.triturus_b200_lm2exp_plan(32, 1024, 1024, 1024, 0, 100000) == 102566
     assert L.triturus_b200_lm2exp_launches(32, 1024, 1024, 1024, 0, 0) == 3
     assert L.triturus_b200_lm2exp_chain_launches(32, 1024, 1024, 1024, 0, 0, 1, 0) == 1

@@ -398,6 +398,7 @@ struct Lm2expPlan {
   bool optimistic;  // ... without a pre-pass: stabiliser from the first k-block, exact passes as conditional launches (2567)
   bool fused;   // max pass inside the contraction kernel (no pre-pass launch)
   bool optimistic_fused;  // ... over the first k-block of each slab only, exact pass as a conditional launch
+  bool optimistic_prepass;  // pair tile in shared memory: pre-pass over the first 32 rows, exact passes conditional
   bool colmax_exclusive;  // one row tile covers I: column maxima of the result are stored, not reduced
   bool promote_tf32;      // plain TF32 over more than kLongContraction terms: accumulator re-summed in chunks
 };
@@ -412,10 +413,11 @@ constexpr int64_t kLongContraction = 32768;
 static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant, Lm2expPlan* out,
                        bool have_m = false, bool b_km = false, bool single_cta = false) {
   if (variant < 0) return TRITURUS_B200_EINVAL;
-  // 0 = automatic, 1 = pre-pass, 2 = fused max pass, 3 = fused max pass over the first k-block only (optimistic)
+  // 0 = automatic, 1 = pre-pass, 2 = fused max pass, 3 = fused max pass over the first k-block only (optimistic),
+  // 4 = pre-pass over the first 32 rows only (optimistic; shared-memory pair tile)
   const int stab_mode = variant / 100000;
   int tile_variant = variant % 100000;
-  if (stab_mode > 3 || (have_m && stab_mode >= 2)) return TRITURUS_B200_EINVAL;
+  if (stab_mode > 4 || (have_m && stab_mode >= 2)) return TRITURUS_B200_EINVAL;
   if (tile_variant == 0) {
     // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
     // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
@@ -424,11 +426,13 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
-    const bool want_pair = !b_km && !single_cta && stab_mode < 2 && !long_3x && !long_tf && I > 256 && K > 128 &&
+    const bool want_pair = !b_km && !single_cta && (stab_mode < 2 || stab_mode == 4) && !long_3x && !long_tf && I > 256 && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
-    const int pair_variant = precision == TRITURUS_B200_PRECISION_TF32 ? (stab_mode == 0 && !have_m ? 2567 : 2566) : 2564;
+    const int pair_variant = precision != TRITURUS_B200_PRECISION_TF32 || stab_mode == 4 ? 2564
+                             : (stab_mode == 0 && !have_m ? 2567 : 2566);
+    if (stab_mode == 4 && !want_pair) return TRITURUS_B200_EINVAL;
     tile_variant = want_pair ? pair_variant : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
   if (b_km && (tile_variant == 2564 || tile_variant == 2566 || tile_variant == 2567 || stab_mode >= 2))
@@ -444,13 +448,14 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   const int mt = tile_variant % 10;
   const bool pair = tile_variant == 2564;  // 256 x 256 tile on a pair of CTAs, 128 rows each
   if (!pair && ((bn != 128 && bn != 256) || (mt != 1 && mt != 2))) return TRITURUS_B200_EINVAL;
-  if (pair && stab_mode >= 2) return TRITURUS_B200_EINVAL;  // the pair kernel takes m from the pre-pass
+  if (pair && (stab_mode == 2 || stab_mode == 3)) return TRITURUS_B200_EINVAL;  // the pair kernels take m from a pre-pass
+  if (stab_mode == 4 && (!pair || tspair)) return TRITURUS_B200_EINVAL;
   if (!pair && precision == TRITURUS_B200_PRECISION_3XTF32) bn = 128;  // hi/lo copies leave room for 128 columns
   // Fused max pass when every column slab of b feeds a single row tile: b then crosses HBM once.  Also when
   // the whole problem is less than one wave of tiles: a second launch then costs more than the row tiles of a
   // slab each scanning it (cfg1: 18.5 us against 21.7 us).
   const bool one_wave = tile_count(R, I, K, bn, mt) <= sm_count();
-  const bool fused = !pair && !b_km && (stab_mode >= 2 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
+  const bool fused = !pair && !b_km && (stab_mode == 2 || stab_mode == 3 || (stab_mode == 0 && (I <= 128 * mt || one_wave)));
   // Such shapes are bound by HBM and by the epilogue: prefer 128 columns, whose accumulator is
   // double-buffered so that the epilogue overlaps the next tile.
   if (fused && variant % 100000 == 0 && bn == 256 && tile_count(R, I, K, 128, mt) >= sm_count()) bn = 128;
@@ -468,6 +473,9 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
       out->fused && (stab_mode == 3 || (stab_mode == 0 && precision == TRITURUS_B200_PRECISION_TF32 && J >= 128 &&
                                         tile_count(R, I, K, bn, mt) > sm_count()));
   out->colmax_exclusive = !pair && I <= 128 * mt;
+  // The shared-memory pair kernel, where it is the automatic choice (3xTF32): the pre-pass scans 32 rows instead of J.
+  out->optimistic_prepass = pair && !tspair && !have_m && J >= 128 &&
+                            (stab_mode == 4 || (stab_mode == 0 && variant % 100000 == 0));
   out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
   return TRITURUS_B200_OK;
 }
@@ -551,7 +559,7 @@ int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, in
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
   // optimistic stabiliser: the contraction and the two conditional launches of the exact passes
-  return plan.fused ? (plan.optimistic_fused ? 3 : 1) : (plan.optimistic ? 3 : 2);
+  return plan.fused ? (plan.optimistic_fused ? 3 : 1) : (plan.optimistic ? 3 : (plan.optimistic_prepass ? 4 : 2));
 }
 
 int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
@@ -561,7 +569,8 @@ int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int pr
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
-  return (plan.fused ? (plan.optimistic_fused ? 3 : 2) : (plan.optimistic ? 0 : 1)) * 100000 + plan.bn * 10 +
+  return (plan.fused ? (plan.optimistic_fused ? 3 : 2) : (plan.optimistic ? 0 : (plan.optimistic_prepass ? 4 : 1))) * 100000 +
+         plan.bn * 10 +
          (plan.tspair ? (plan.optimistic ? 7 : 6) : plan.mt);
 }
 
@@ -757,6 +766,24 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     p.reset_flag = flag;
     return launch_lm2exp_tspair<LmTsPair>(ta, tb_plain, to, p, st, true);
   }
+  if (pair && !use_ts && plan.optimistic_prepass && prepass && ws_flags && out_colmax == nullptr) {
+    // Pre-pass over the first 32 rows of b only; the contraction raises the flag if a result overflowed, and the
+    // full pre-pass and the contraction with its maxima follow as launches that return at once unless it did.
+    int* flag = static_cast<int*>(workspace);
+    rc = colmax_run(b, m_buf, R, std::min<int64_t>(J, 32), K, bstr, stream, nullptr, nullptr);
+    if (rc != TRITURUS_B200_OK) return rc;
+    Lm2expParams po = p;
+    po.opt_flag = flag;
+    rc = precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, po, st, true)
+                                                      : launch_lm2exp_pair<LmPairT>(ta, tb, to, po, st, true);
+    if (rc != TRITURUS_B200_OK) return rc;
+    rc = colmax_run(b, m_buf, R, J, K, bstr, stream, flag, flag + 1);
+    if (rc != TRITURUS_B200_OK) return rc;
+    p.only_if = flag + 1;
+    p.reset_flag = flag;
+    return precision == TRITURUS_B200_PRECISION_3XTF32 ? launch_lm2exp_pair<LmPairX>(ta, tb, to, p, st, true)
+                                                        : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st, true);
+  }
   if (prepass && b_km) {
     for (int64_t r0 = 0; r0 < R; r0 += 65535) {  // (R <= 65535 here: one round)
       const dim3 grid(static_cast<unsigned>((K + 7) / 8), static_cast<unsigned>(std::min<int64_t>(65535, R - r0)));
@@ -915,6 +942,7 @@ int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan, have_b_colmax != 0);
   if (rc != TRITURUS_B200_OK) return rc;
   if ((plan.optimistic || plan.optimistic_fused) && !want_out_colmax) return 3;  // as triturus_b200_lm2exp_launches
+  if (plan.optimistic_prepass && !want_out_colmax) return 4;
   return 1 + ((plan.fused || have_b_colmax) ? 0 : 1) + ((want_out_colmax && !plan.colmax_exclusive) ? 1 : 0);
 }
 

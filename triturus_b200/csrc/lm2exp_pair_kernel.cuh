@@ -54,6 +54,14 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BNH = Cfg::BNH, BK = Cfg::BK, NS = Cfg::NS;
   constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP;
 
+  // A conditional launch: runs only if the launch before it left the word up (same value for every thread of
+  // both CTAs, read before any barrier or allocation exists).
+  if (p.only_if != nullptr) {
+    pdl_wait();
+    if (*p.only_if == 0) return;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.reset_flag != nullptr) *p.reset_flag = 0;  // all its readers are done
+  }
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
@@ -216,6 +224,10 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     pdl_wait();  // m comes from the pre-pass, which may still be running when this kernel starts
     uint32_t tcount = 0, nblk = 0;  // tiles seen; staging boxes handed to the fold warp so far
     bool ok = true;
+    // Optimistic pre-pass (the stabilisers are the column maxima over the first 32 rows only): a result that
+    // overflowed raises *opt_flag and the caller's conditional launches redo the call with the exact maxima.
+    const bool opt = p.opt_flag != nullptr;
+    bool overflowed = false;
     const bool emit_max = p.out_max != nullptr;
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
@@ -263,6 +275,10 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
               const float acc = __uint_as_float(v[h][e]);
               o[e] = m_e + (PREC ? logf(acc) : lg2_approx(acc) * LN2_F);
             }
+            if (opt) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) overflowed |= !(o[e] < INFINITY);  // +inf or NaN
+            }
             // swizzled 32 x 32 staging box, then TMA store or row-wise stores (see lm2exp_kernel.cuh)
             // the fold warp (column maxima of the result) has read the previous box
             if (emit_max && nblk > 0 &&
@@ -308,6 +324,7 @@ lm2exp_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       }
     }
     if (use_tma && lane == 0) tma_store_wait_all();
+    if (opt && __any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
   } else if (warp >= 2 && warp < 4 && p.out_max != nullptr) {
     // ------------------------------------------------------------------ fold: column maxima of the result
     // As in lm2exp_kernel.cuh: warp 2 serves epilogue warps 4 and 5, warp 3 serves 6 and 7.  The other CTA of
