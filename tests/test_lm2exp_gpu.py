@@ -239,15 +239,20 @@ def test_optimistic_fused_max_pass(case, precision, tile):
 
 
 def test_optimistic_fused_max_pass_is_automatic_for_long_tf32_launches():
-    """cfg3's shape: plain TF32 takes the optimistic max pass, 3xTF32 and short or small problems the full one."""
+    """One 128-row block, long launch: plain TF32 takes the optimistic max pass, 3xTF32 and short or small problems
+    the full one.  From two row blocks on (cfg3) the pair kernels with their optimistic stabilisers take over."""
     from triturus_b200 import _native
 
     L = _native.LIB
-    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 0, 0) == 301282
-    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 1, 0) == 201282
+    assert L.triturus_b200_lm2exp_plan(256, 128, 256, 8192, 0, 0) // 100000 == 3
+    assert L.triturus_b200_lm2exp_plan(256, 128, 256, 8192, 1, 0) // 100000 == 2
+    assert L.triturus_b200_lm2exp_launches(256, 128, 256, 8192, 0, 0) == 3
     assert L.triturus_b200_lm2exp_plan(4, 256, 256, 256, 0, 0) == 201281  # cfg1: less than one wave
-    assert L.triturus_b200_lm2exp_plan(128, 256, 64, 8192, 0, 0) // 100000 == 2  # two k-blocks: nothing to save
-    assert L.triturus_b200_lm2exp_launches(128, 256, 256, 8192, 0, 0) == 3
+    assert L.triturus_b200_lm2exp_plan(256, 128, 64, 8192, 0, 0) // 100000 == 2  # two k-blocks: nothing to save
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 0, 0) == 2567  # cfg3
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 1, 0) == 402564
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 0, 100000) % 10 == 2  # forced pre-pass: a single-CTA tile as before
+    assert L.triturus_b200_lm2exp_plan(128, 256, 256, 8192, 0, 200000) == 201282
     assert L.triturus_b200_lm2exp_chain_launches(128, 256, 256, 8192, 0, 300000, 1, 0) < 0  # stabiliser supplied
 
 

@@ -419,14 +419,18 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   int tile_variant = variant % 100000;
   if (stab_mode > 4 || (have_m && stab_mode >= 2)) return TRITURUS_B200_EINVAL;
   if (tile_variant == 0) {
-    // More than one 256-row tile per column slab: the stabiliser comes from the pre-pass anyway, and a CTA
-    // pair moves the fewest shared-memory bytes per MAC.  Otherwise a single-CTA tile with the fused max pass.
+    // More than one 256-row tile per column slab: the stabiliser comes from a pre-pass anyway, and a CTA
+    // pair moves the fewest shared-memory bytes per MAC.  With the optimistic stabilisers, which need no full
+    // pre-pass, the pair kernels also win from two 128-row blocks on (cfg3, I = 256: 0.479 ms on the
+    // TMEM-operand pair kernel against 0.508 ms on the single-CTA kernel with the optimistic fused max pass; in
+    // 3xTF32 1.14 against 1.30 ms).  Otherwise a single-CTA tile with the fused max pass.
     // (Not for 3xTF32 contractions longer than 4096, where the drift of the tensor core's truncating
     // accumulator, ~1.2e-8 per term, would use up the 3xTF32 tolerance: only the single-CTA kernel re-sums
     // its accumulator in chunks.)
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
-    const bool want_pair = !b_km && !single_cta && (stab_mode < 2 || stab_mode == 4) && !long_3x && !long_tf && I > 256 && K > 128 &&
+    const bool want_pair = !b_km && !single_cta && (stab_mode < 2 || stab_mode == 4) && !long_3x && !long_tf &&
+                           (I > 256 || (I > 128 && J >= 128 && !have_m && stab_mode != 1)) && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
