@@ -25,7 +25,7 @@ namespace tb200 {
 // folds the four row slots with warp shuffles.
 template <bool VEC>
 __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x, float* __restrict__ m, int J, int K,
-                                                      int64_t s0, int64_t s1, int64_t s2, const int* only_if,
+                                                      int64_t s0, int64_t s1, int64_t s2, int R, const int* only_if,
                                                       int* publish) {
   __shared__ float part[8][32];
   // The contraction kernel that consumes m may be launched as a programmatic dependent: let it start its set-up
@@ -38,12 +38,18 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
   if (only_if != nullptr) {
     pdl_wait();
     const bool up = *only_if != 0;
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *publish = up ? 1 : 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *publish = up ? 1 : 0;
     if (!up) return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.y;
-  const int c0 = blockIdx.x * 32;
+  // Work items (32-column block, batch entry) are walked with a grid stride: an ordinary launch has one block per
+  // item, a conditional one a few blocks per SM (thousands of blocks that only read the flag and leave would
+  // cost tens of microseconds on every call).
+  const int nbx = (K + 31) / 32;
+  const int64_t items = static_cast<int64_t>(nbx) * R;
+  for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+  const int r = static_cast<int>(item / nbx);
+  const int c0 = static_cast<int>(item % nbx) * 32;
   const float* xb = x + static_cast<int64_t>(r) * s0;
   if (VEC) {
     const int cg = lane & 7, rs = lane >> 3;
@@ -86,6 +92,8 @@ __global__ void __launch_bounds__(256) colmax_kernel(const float* __restrict__ x
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, part[w][lane]);
     const int c = c0 + lane;
     if (c < K) m[static_cast<int64_t>(r) * K + c] = clamp_stab(mx);
+  }
+  __syncthreads();  // `part` is rewritten by the next item
   }
 }
 
@@ -528,26 +536,20 @@ int triturus_b200_selftest_wait_timeout(int32_t* status_dev, int64_t limit_cycle
 static int colmax_run(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
                       void* stream, const int* only_if, int* publish) {
   if (x == nullptr || m == nullptr || x_strides == nullptr) return TRITURUS_B200_EINVAL;
-  if (R <= 0 || J <= 0 || K <= 0 || J > INT32_MAX || K > INT32_MAX) return TRITURUS_B200_EINVAL;
-  if (R > 65535) {  // gridDim.y holds the batch: block by block beyond its limit
-    for (int64_t r0 = 0; r0 < R; r0 += 65535) {
-      const int rc = colmax_run(x + r0 * x_strides[0], m + r0 * K, R - r0 < 65535 ? R - r0 : 65535, J, K, x_strides,
-                                stream, only_if, publish);
-      if (rc != TRITURUS_B200_OK) return rc;
-    }
-    return TRITURUS_B200_OK;
-  }
+  if (R <= 0 || J <= 0 || K <= 0 || J > INT32_MAX || K > INT32_MAX || R > INT32_MAX) return TRITURUS_B200_EINVAL;
   const int64_t s2 = K > 1 ? x_strides[2] : 1;
   const bool vec = s2 == 1 && (K & 3) == 0 && aligned16(x) && (x_strides[0] & 3) == 0 && (x_strides[1] & 3) == 0;
-  const dim3 grid(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>(R));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // (a conditional launch follows the optimistic contraction as its programmatic dependent)
+  const int64_t items = ((K + 31) / 32) * R;
+  // (a conditional launch follows the optimistic contraction as its programmatic dependent, with few blocks)
   const bool dep = only_if != nullptr;
-  const int Ji = static_cast<int>(J), Ki = static_cast<int>(K);
+  const int64_t cap = dep ? static_cast<int64_t>(sm_count()) * 8 : static_cast<int64_t>(INT32_MAX);
+  const dim3 grid(static_cast<unsigned>(items < cap ? items : cap));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Ji = static_cast<int>(J), Ki = static_cast<int>(K), Ri = static_cast<int>(R);
   return vec ? launch_maybe_dependent(colmax_kernel<true>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
-                                      s2, only_if, publish)
+                                      s2, Ri, only_if, publish)
              : launch_maybe_dependent(colmax_kernel<false>, grid, 256, 0, st, dep, x, m, Ji, Ki, x_strides[0], x_strides[1],
-                                      s2, only_if, publish);
+                                      s2, Ri, only_if, publish);
 }
 
 int triturus_b200_colmax_f32(const float* x, float* m, int64_t R, int64_t J, int64_t K, const int64_t x_strides[3],
