@@ -287,6 +287,16 @@ using LmX_128_2 = Lm2expCfg<128, 2, 1, 2>;
 using LmP_128_1 = Lm2expCfg<128, 1, 0, 6, true>;
 using LmP_128_2 = Lm2expCfg<128, 2, 0, 4, true>;
 
+// the same tiles with the paths for a transposed b and for operands fetched element by element
+using LmTo_128_1 = Lm2expCfg<128, 1, 0, 6, false, false, true>;
+using LmTo_128_2 = Lm2expCfg<128, 2, 0, 4, false, false, true>;
+using LmTo_256_1 = Lm2expCfg<256, 1, 0, 4, false, false, true>;
+using LmTo_256_2 = Lm2expCfg<256, 2, 0, 3, false, false, true>;
+using LmXo_128_1 = Lm2expCfg<128, 1, 1, 3, true, false, true>;
+using LmXo_128_2 = Lm2expCfg<128, 2, 1, 2, true, false, true>;
+using LmPo_128_1 = Lm2expCfg<128, 1, 0, 6, true, false, true>;
+using LmPo_128_2 = Lm2expCfg<128, 2, 0, 4, true, false, true>;
+
 // plain matrix product (the reference's mm): 256 x 128 tiles, no stabiliser / exp / log
 using LmPlainT = Lm2expCfg<128, 2, 0, 4, false, true>;
 using LmPlainX = Lm2expCfg<128, 2, 1, 2, true, true>;
@@ -435,15 +445,19 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
     // (Not for 3xTF32 contractions longer than 4096, where the drift of the tensor core's truncating
     // accumulator, ~1.2e-8 per term, would use up the 3xTF32 tolerance: only the single-CTA kernel re-sums
     // its accumulator in chunks.)
+    // The optimistic forms cost two or three launches more, which return at once on the device but take the host
+    // some 7 us per call: below ~50 us of work a loop of calls would wait for the host (R64 256^3: 14.4 us per
+    // call on the device but 24 us in an eager loop, against 18.3 / 17.7 us for the single launch).
+    const bool big = 2.0 * static_cast<double>(R) * I * J * K >= 2e10;
     const bool long_3x = precision == TRITURUS_B200_PRECISION_3XTF32 && J > 4096;
     const bool long_tf = precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
     const bool want_pair = !b_km && !single_cta && (stab_mode < 2 || stab_mode == 4) && !long_3x && !long_tf &&
-                           (I > 256 || (I > 128 && J >= 128 && !have_m && stab_mode != 1)) && K > 128 &&
+                           (I > 256 || (I > 128 && J >= 128 && !have_m && stab_mode != 1 && big)) && K > 128 &&
                            tile_count(R, I, K, 256, 2) >= sm_count() / 4;
     // (long plain-TF32 contractions: 128 columns, so that the master copy fits beside the accumulator)
     // Plain TF32 on pairs: the TMEM-operand kernel, with the optimistic stabiliser unless a pre-pass was asked for.
     const int pair_variant = precision != TRITURUS_B200_PRECISION_TF32 || stab_mode == 4 ? 2564
-                             : (stab_mode == 0 && !have_m ? 2567 : 2566);
+                             : (stab_mode == 0 && !have_m && big ? 2567 : 2566);
     if (stab_mode == 4 && !want_pair) return TRITURUS_B200_EINVAL;
     tile_variant = want_pair ? pair_variant : auto_variant(R, I, K, precision == TRITURUS_B200_PRECISION_TF32 && !long_tf, true);
   }
@@ -481,13 +495,14 @@ static int plan_lm2exp(int64_t R, int64_t I, int64_t J, int64_t K, int precision
   // enough (more than one wave of tiles) for two more, empty, launches not to matter.
   // Plain TF32 only: in 3xTF32 the shapes concerned are bound by the three MMAs per k-step, not by the max pass
   // (cfg3: 1.35 ms with, 1.32 ms without).
+  const bool big_enough = 2.0 * static_cast<double>(R) * I * J * K >= 2e10;  // (see `big` above)
   out->optimistic_fused =
       out->fused && (stab_mode == 3 || (stab_mode == 0 && precision == TRITURUS_B200_PRECISION_TF32 && J >= 128 &&
-                                        tile_count(R, I, K, bn, mt) > sm_count()));
+                                        big_enough && tile_count(R, I, K, bn, mt) > sm_count()));
   out->colmax_exclusive = !pair && I <= 128 * mt;
   // The shared-memory pair kernel, where it is the automatic choice (3xTF32): the pre-pass scans 32 rows instead of J.
   out->optimistic_prepass = pair && !tspair && !have_m && J >= 128 &&
-                            (stab_mode == 4 || (stab_mode == 0 && variant % 100000 == 0));
+                            (stab_mode == 4 || (stab_mode == 0 && variant % 100000 == 0 && big_enough));
   out->promote_tf32 = !pair && bn == 128 && precision == TRITURUS_B200_PRECISION_TF32 && J > kLongContraction;
   return TRITURUS_B200_OK;
 }
@@ -807,6 +822,20 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
                                                         : launch_lm2exp_pair<LmPairT>(ta, tb, to, p, st, dep);
   }
   auto single = [&](const Lm2expParams& q, bool dependent) -> int {
+    if (b_km || gen_a || gen_b) {
+      if (precision == TRITURUS_B200_PRECISION_3XTF32) {
+        return mt == 2 ? launch_lm2exp<LmXo_128_2>(ta, tb, to, q, st, dependent)
+                       : launch_lm2exp<LmXo_128_1>(ta, tb, to, q, st, dependent);
+      }
+      if (bn == 256)
+        return mt == 2 ? launch_lm2exp<LmTo_256_2>(ta, tb, to, q, st, dependent)
+                       : launch_lm2exp<LmTo_256_1>(ta, tb, to, q, st, dependent);
+      if (plan.promote_tf32)
+        return mt == 2 ? launch_lm2exp<LmPo_128_2>(ta, tb, to, q, st, dependent)
+                       : launch_lm2exp<LmPo_128_1>(ta, tb, to, q, st, dependent);
+      return mt == 2 ? launch_lm2exp<LmTo_128_2>(ta, tb, to, q, st, dependent)
+                     : launch_lm2exp<LmTo_128_1>(ta, tb, to, q, st, dependent);
+    }
     if (precision == TRITURUS_B200_PRECISION_3XTF32) {
       return mt == 2 ? launch_lm2exp<LmX_128_2>(ta, tb, to, q, st, dependent)
                      : launch_lm2exp<LmX_128_1>(ta, tb, to, q, st, dependent);

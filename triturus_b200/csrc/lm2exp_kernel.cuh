@@ -63,8 +63,13 @@ struct Lm2expParams {
 // PLAIN_ = true turns the kernel into a plain batched matrix product out = a * b (the reference's `mm`,
 // triturus/mm.py:181-214): no stabiliser, no exp, no log; in the single-pass TF32 mode both operands are rounded
 // to nearest tf32 as the reference's kernel does with cvt.rna (triturus/mm.py:152-154, triturus/utils.py:56-63).
-template <int BN_, int MT_, int PREC_, int NS_, bool PROMOTE_ = (PREC_ != 0), bool PLAIN_ = false>
+// ODD_ = true adds the paths for operands in other layouts: a transposed b (p.b_km) and operands fetched element
+// by element (p.gen_a / p.gen_b).  They are a template switch, not only run-time branches, because the kernel is
+// sensitive to its code size: with those paths compiled into every instance the ordinary ones ran 5-14 % slower
+// (cfg3 on the 128 x 2 tile with the full max pass 0.61 -> 0.70 ms, cfg1 at R = 64 20.6 -> 22.6 us).
+template <int BN_, int MT_, int PREC_, int NS_, bool PROMOTE_ = (PREC_ != 0), bool PLAIN_ = false, bool ODD_ = false>
 struct Lm2expCfg {
+  static constexpr bool ODD = ODD_;
   static constexpr int BM = 128, BK = 32, NTW = 8;
   static constexpr int BN = BN_, MT = MT_, PREC = PREC_, NS = NS_;
   static constexpr bool PLAIN = PLAIN_;
@@ -111,6 +116,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               const __grid_constant__ CUtensorMap tmap_out, const Lm2expParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, MT = Cfg::MT, NS = Cfg::NS;
   constexpr int PREC = Cfg::PREC, NTW = Cfg::NTW, NGRP = Cfg::NGRP, RP = Cfg::RP;
+  // operands in other layouts (only instances built with ODD carry the code)
+  const bool b_km = Cfg::ODD && p.b_km != 0;
+  const bool gen_a = Cfg::ODD && p.gen_a != 0, gen_b = Cfg::ODD && p.gen_b != 0;
 
   // A conditional launch: runs only if the launch before it left the word up (same value for every thread,
   // read before any barrier or allocation exists).
@@ -156,7 +164,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full[s], 1 + ((p.gen_a || p.gen_b) ? 64 : 0));  // + the 64 threads of the element-wise loader
+      mbar_init(&full[s], 1 + ((gen_a || gen_b) ? 64 : 0));  // + the 64 threads of the element-wise loader
       mbar_init(&xf_done[s], NTW);
       mbar_init(&stage_empty[s], 1);
     }
@@ -172,8 +180,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&box_free[s], 1);
     }
     fence_mbar_init();
-    if (!p.gen_a) tma_prefetch_desc(&tmap_a);  // (a tensor map that is not used is all zeros)
-    if (!p.gen_b) tma_prefetch_desc(&tmap_b);
+    if (!gen_a) tma_prefetch_desc(&tmap_a);  // (a tensor map that is not used is all zeros)
+    if (!gen_b) tma_prefetch_desc(&tmap_b);
     if (p.out_tma) tma_prefetch_desc(&tmap_out);
   }
   if (warp == 1) {
@@ -228,8 +236,8 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const int s = it % NS;
             const uint32_t ph = (it / NS) & 1;
             if (!(ok = mbar_wait(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
-            mbar_arrive_expect_tx(&full[s], ((pass && !p.gen_a) ? MT * Cfg::A_TILE : 0) + (p.gen_b ? 0 : Cfg::B_TILE));
-            if (pass && !p.gen_a) {
+            mbar_arrive_expect_tx(&full[s], ((pass && !gen_a) ? MT * Cfg::A_TILE : 0) + (gen_b ? 0 : Cfg::B_TILE));
+            if (pass && !gen_a) {
               if (p.a_mn) {
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
@@ -242,13 +250,13 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 for (int t = 0; t < MT; ++t) tma_load_3d(a_tile(s, 0, t), &tmap_a, &full[s], kb * BK, i0 + t * BM, r);
               }
             }
-            if (pass && prefetch_next && !p.gen_b) {
+            if (pass && prefetch_next && !gen_b) {
 #pragma unroll
               for (int g = 0; g < NGRP; ++g) tma_prefetch_l2_3d(&tmap_b, nn0 + g * 32, kb * BK, nr);
             }
-            if (p.gen_b) {
+            if (gen_b) {
               // (warps 2-3 fetch the b tile)
-            } else if (p.b_km) {
+            } else if (b_km) {
               tma_load_3d(b_tile(s, 0), &tmap_b, &full[s], kb * BK, n0, r);  // rows k of 32 j: the layout of an a tile
             } else {
 #pragma unroll
@@ -264,9 +272,9 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // B operand is MN-major; A too when a is a transposed view (bit 15)
-      const uint32_t idesc = umma_idesc_tf32(BM, BN) | (p.b_km ? 0u : (1u << 16)) | (p.a_mn ? (1u << 15) : 0u);
+      const uint32_t idesc = umma_idesc_tf32(BM, BN) | (b_km ? 0u : (1u << 16)) | (p.a_mn ? (1u << 15) : 0u);
       const uint32_t a_step = p.a_mn ? 64u : 2u;  // encoded address step per 8 contraction values
-      const uint32_t b_step = p.b_km ? 2u : 64u;  // K-major: 32 bytes along the row; MN-major: eight 128-byte rows
+      const uint32_t b_step = b_km ? 2u : 64u;  // K-major: 32 bytes along the row; MN-major: eight 128-byte rows
       uint32_t it = 0, ccount = 0;  // k-block stages and accumulation chunks issued so far
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -294,10 +302,10 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             if (!(ok = mbar_wait(&full[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
             if (!(ok = mbar_wait(&xf_done[s], ph, ctl, STATUS_TIMEOUT_MMA))) break;
             tc_fence_after_sync();
-            const uint64_t db_hi = p.b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 0)))
+            const uint64_t db_hi = b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 0)))
                                           : umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 0)), Cfg::B_BOX);
             const uint64_t db_lo = !PREC ? 0
-                                   : p.b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 1)))
+                                   : b_km ? umma_desc_k_sw128(smem_u32(b_tile(s, 1)))
                                             : umma_desc_mn_sw128_base32(smem_u32(b_tile(s, 1)), Cfg::B_BOX);
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
@@ -483,7 +491,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
     if (opt && __any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
-  } else if (warp >= 2 && warp < 4 && (p.gen_a || p.gen_b)) {
+  } else if (warp >= 2 && warp < 4 && (gen_a || gen_b)) {
     // ------------------------------------------------------------------ element-wise loader (never with out_max)
     // Walks the stages exactly as the TMA producer does and fills the tiles of the operands it is responsible
     // for.  A stage is reported `LAG` stages late: each thread waits for its own copies of that stage
@@ -503,7 +511,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           const uint32_t ph = (it / NS) & 1;
           if (!(ok = mbar_wait_warp(&stage_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
           const int j0 = kb * BK;
-          if (pass && p.gen_a) {
+          if (pass && gen_a) {
             // a tile: 128 x MT rows i of 32 values j, K-major, 128-byte swizzle; consecutive threads consecutive j
             for (int e = lt; e < MT * BM * BK; e += 64) {
               const int row = e >> 5, j = e & 31;
@@ -513,7 +521,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               cp_async_f32(smem_u32(a_tile(s, 0, t)) + sw128_offset(rr, j), valid ? src : p.a_ptr, valid);
             }
           }
-          if (p.gen_b) {
+          if (gen_b) {
             // b tile: 32 rows j of BN values k in boxes of 32 columns; consecutive threads consecutive k
             for (int e = lt; e < BK * BN; e += 64) {
               const int j = e / BN, k = e % BN;
@@ -649,7 +657,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       } else if (Cfg::PLAIN) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) m4[x] = 0.f;  // plain product: no stabiliser
-      } else if (p.b_km) {
+      } else if (b_km) {
         m4[0] = (n0 + krow < p.K) ? clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + n0 + krow)) : 0.f;
         m4[1] = m4[2] = m4[3] = m4[0];
       } else {
@@ -660,7 +668,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
       // publish the stabiliser of this tile's columns for the epilogue
       const int slot = tcount & 1;
-      if (p.b_km) {
+      if (b_km) {
         if (kpart == 0) {  // (whole warps: BN is a multiple of 32)
           if (!(ok = mbar_wait_warp(&msum_empty[slot], ((tcount >> 1) & 1) ^ 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
           msum[slot * BN + krow] = m4[0];
@@ -683,7 +691,7 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         uint8_t* box_lo = b_tile(s, PREC ? 1 : 0) + grp * Cfg::B_BOX;
         const int jrem = p.J - kb * BK;
         constexpr int NLD = Cfg::ROWS_PER_WARP / 4;
-        if (p.b_km) {
+        if (b_km) {
           // Row krow of the tile is column n0 + krow of b with its 32 values j of this k-block: eight 16-byte
           // pieces, piece i at (i ^ (krow & 7)) * 16 of the 128-byte row.  Eight consecutive lanes read the same
           // piece index of eight consecutive rows, which the swizzle spreads over all 32 banks.
