@@ -133,7 +133,9 @@ int triturus_b200_lm2exp_chain_f32(const float* a, const float* b, float* out, i
  * column maxima of a and b.
  * Replaces triturus/lt2exp.py:519-630 (host wrapper), :227-357 (_ker_lt2exp_unsplit) and :365-506
  * (_ker_lt2exp_split); semantics follow baselines/lt2exp.py:4-25.
- *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].
+ *   w [R,S,I,J], a [R,I,K], b [R,J,K], out [R,S,K].  w follows the general rules above (it goes through a tensor
+ *   map); a and b are read with ordinary loads and may have any strides (triturus/lt2exp.py:580-585, :612-617
+ *   forward whatever they are given): 16 bytes at a time when base and strides allow it, else 4.
  *   variant: 0 = automatic, otherwise SPLIT * 10000 + BN * 10 + MT with BN * 10 + MT as above (0 = automatic;
  *            additionally, TF32 only, the generated operand kept in tensor memory instead of shared memory:
  *            1283 / 1284 = tile of 128 columns x 128 / 256 rows, 1285 = 256 columns x 128 rows, which the

@@ -411,3 +411,33 @@ def test_batches_beyond_the_grid_limit():
     for variant in (10000, 2 * 10000):
         got = _run(w, a, b, precision="3xtf32", variant=variant)
         _assert_close(got, w, a, b, "3xtf32")
+
+
+@pytest.mark.parametrize("variant", [0, 11281, 11282, 12561, 11283, 11285, 99981281])
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32"])
+def test_strided_views_of_a_and_b_are_read_in_place(precision, variant):
+    """a and b as transposed views (k stride = I resp. J), as every second column of a wider tensor, and broadcast over
+    the batch (stride 0): the reference forwards any strides (triturus/lt2exp.py:580-585, :612-617) and so does the
+    C ABI; no copy is made on the way."""
+    import triturus_b200 as tb
+
+    if precision == "3xtf32" and variant in (12561, 11283, 11285):
+        pytest.skip("tile not available in 3xTF32")
+    g = torch.Generator().manual_seed(31 + variant)
+    R, S, I, J, K = 3, 70, 12, 20, 300
+    w = torch.rand(R, S, I, J, generator=g)
+    a_t = (torch.randn(R, K, I, generator=g) * 3.0).cuda()      # stored [R, K, I]
+    b_wide = (torch.randn(R, J, 2 * K + 1, generator=g) * 3.0).cuda()
+    a_v, b_v = a_t.transpose(1, 2), b_wide[:, :, 1::2][:, :, :K]
+    a_v[0, :, 5] = float("-inf")
+    got = tb.lt2exp(w.cuda(), a_v, b_v, precision=precision, variant=variant)
+    tb.check_status()
+    want = orc.lt2exp_fp64(w, a_v.cpu().contiguous(), b_v.cpu().contiguous())
+    res = orc.compare_logspace(got.cpu(), want, ATOL[precision])
+    assert res["ok"], res
+    assert torch.all(got[0, :, 5] == float("-inf"))
+    b_b = (torch.randn(1, J, K, generator=g) * 3.0).cuda().expand(R, J, K)  # the same b for every batch entry
+    got = tb.lt2exp(w.cuda(), a_v, b_b, precision=precision, variant=variant)
+    tb.check_status()
+    res = orc.compare_logspace(got.cpu(), orc.lt2exp_fp64(w, a_v.cpu().contiguous(), b_b.cpu().contiguous()), ATOL[precision])
+    assert res["ok"], res

@@ -286,20 +286,10 @@ def _lm2exp_b_operand(b: torch.Tensor, variant: int, flop: float = float("inf"),
     return _tma_ready(b)
 
 
-def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
-    """Return `t` or a contiguous copy when its innermost stride is not 1 or a stride is not positive."""
-    if (t.shape[-1] == 1 or t.stride(-1) == 1) and all(
-        t.shape[d] == 1 or t.stride(d) > 0 for d in range(t.dim() - 1)
-    ):
-        return t
-    return t.contiguous()
-
-
 def colmax(x: torch.Tensor) -> torch.Tensor:
     """Clamped column maximum of x[R, J, K] over J -> [R, K] (the stabiliser pre-pass)."""
     _require_cuda(x)
-    x = _inner_contiguous(x)
-    R, J, K = x.shape
+    R, J, K = x.shape  # (any strides: the kernel reads 16 bytes at a time where they allow it, else 4)
     m = torch.empty((R, K), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
@@ -395,8 +385,8 @@ def _lt2exp_impl(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, precision: i
     R, S, I, J = w.shape
     K = a.shape[2]
     w = _tma_ready(w)
-    a = _inner_contiguous(a)
-    b = _inner_contiguous(b)
+    # a and b are read with ordinary loads and go in as they are, whatever their strides (16-byte loads when they
+    # allow it; a view with a k stride other than 1 is read 4 bytes at a time, uncoalesced but without a copy)
     out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)
     with _on_device(a.device) as idx:
         # scratch memory for tiles that several CTAs share (the end-to-end form of the contraction split)
@@ -449,8 +439,6 @@ def _lt2exp_chain_impl(
     R, S, I, J = w.shape
     K = a.shape[2]
     w = _tma_ready(w)
-    a = _inner_contiguous(a)
-    b = _inner_contiguous(b)
     a_colmax = _colmax_arg(a_colmax, R, K, a, "a_colmax")
     b_colmax = _colmax_arg(b_colmax, R, K, a, "b_colmax")
     out = torch.empty((R, S, K), dtype=torch.float32, device=a.device)

@@ -1299,14 +1299,16 @@ static int lt2exp_run_block(const float* w, const float* a, const float* b, floa
   int64_t as0 = a_strides[0], as1 = a_strides[1], as2 = a_strides[2];
   int64_t bs0 = b_strides[0], bs1 = b_strides[1], bs2 = b_strides[2];
   int64_t os0 = out_strides[0], os1 = out_strides[1], os2 = out_strides[2];
-  if ((J > 1 && ws3 != 1) || (K > 1 && (as2 != 1 || bs2 != 1 || os2 != 1))) return TRITURUS_B200_EALIGN;
-  if (!aligned16(w)) return TRITURUS_B200_EALIGN;
+  // w goes through a tensor map; a and b are read with ordinary loads, 4 bytes at a time unless vec_ab holds, and
+  // may have any strides (the reference forwards whatever it is given, triturus/lt2exp.py:580-585 and :612-617).
+  if ((J > 1 && ws3 != 1) || (K > 1 && os2 != 1)) return TRITURUS_B200_EALIGN;
+  if (!aligned16(w) || (reinterpret_cast<uintptr_t>(a) & 3) != 0 || (reinterpret_cast<uintptr_t>(b) & 3) != 0)
+    return TRITURUS_B200_EALIGN;
+  if (K == 1) as2 = bs2 = 1;
   const int64_t j4 = round_up4(J);
   if (!fix_stride(I, ws2, j4) || !fix_stride(S, ws1, j4 * I) || !fix_stride(R, ws0, j4 * I * S))
     return TRITURUS_B200_EALIGN;
-  if ((I > 1 && as1 <= 0) || (R > 1 && as0 <= 0) || (J > 1 && bs1 <= 0) || (R > 1 && bs0 <= 0) ||
-      (S > 1 && os1 <= 0) || (R > 1 && os0 <= 0))
-    return TRITURUS_B200_EALIGN;
+  if ((S > 1 && os1 <= 0) || (R > 1 && os0 <= 0)) return TRITURUS_B200_EALIGN;
 
   int bn, mt, split;
   bool promote;
@@ -1332,6 +1334,8 @@ static int lt2exp_run_block(const float* w, const float* a, const float* b, floa
   p.a_s1 = as1;
   p.b_s0 = bs0;
   p.b_s1 = bs1;
+  p.a_s2 = as2;
+  p.b_s2 = bs2;
   p.out_s0 = os0;
   p.out_s1 = os1;
   p.R = static_cast<int>(R);
@@ -1340,8 +1344,8 @@ static int lt2exp_run_block(const float* w, const float* a, const float* b, floa
   p.J = static_cast<int>(J);
   p.K = static_cast<int>(K);
   p.tiles_m = p.tiles_n = p.num_tiles = 0;
-  p.vec_ab = (K % 4 == 0 && aligned16(a) && aligned16(b) && as0 % 4 == 0 && as1 % 4 == 0 && bs0 % 4 == 0 &&
-              bs1 % 4 == 0) ? 1 : 0;
+  p.vec_ab = (K % 4 == 0 && as2 == 1 && bs2 == 1 && aligned16(a) && aligned16(b) && as0 % 4 == 0 && as1 % 4 == 0 &&
+              bs0 % 4 == 0 && bs1 % 4 == 0) ? 1 : 0;
   p.status = status_dev;
   p.ma_in = a_colmax;
   p.mb_in = b_colmax;

@@ -45,7 +45,8 @@ struct Lt2expParams {
   const float* a;  // [R, I, K]
   const float* b;  // [R, J, K]
   float* out;      // [R, S, K]
-  int64_t a_s0, a_s1, b_s0, b_s1;  // element strides (innermost stride is 1)
+  int64_t a_s0, a_s1, b_s0, b_s1;  // element strides of the batch and row dimensions
+  int64_t a_s2 = 1, b_s2 = 1;      // ... and along k (any value; the 16-byte loads of vec_ab need 1)
   int64_t out_s0, out_s1;
   int R, S, I, J, K;
   int tiles_m, tiles_n, num_tiles;
@@ -594,8 +595,8 @@ lt2exp_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParams p) 
       decode(w.tile, r, n0, s0);
       const int kcol = n0 + n;
       const bool col_ok = kcol < p.K;
-      const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
-      const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + kcol;
+      const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + static_cast<int64_t>(kcol) * p.a_s2;
+      const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + static_cast<int64_t>(kcol) * p.b_s2;
 
       // Column maxima over the full I and J, clamped as the reference does (baselines/lt2exp.py:15-19): an
       // all -inf column gets -1e38, its exps are exact zeros and the result is -inf, never NaN.  The transform
@@ -792,8 +793,8 @@ __global__ void __launch_bounds__(256) lt2exp_finish_kernel(const Lt2expParams p
   } else {
     const int n = tid & 127, g = tid >> 7;
     const bool col_ok = k0 + n < p.K;
-    part[0][g][n] = col_ok ? strided_column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + k0 + n, p.a_s1, p.I, g, 2) : -INFINITY;
-    part[1][g][n] = col_ok ? strided_column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + k0 + n, p.b_s1, p.J, g, 2) : -INFINITY;
+    part[0][g][n] = col_ok ? strided_column_max(p.a + static_cast<int64_t>(r) * p.a_s0 + static_cast<int64_t>(k0 + n) * p.a_s2, p.a_s1, p.I, g, 2) : -INFINITY;
+    part[1][g][n] = col_ok ? strided_column_max(p.b + static_cast<int64_t>(r) * p.b_s0 + static_cast<int64_t>(k0 + n) * p.b_s2, p.b_s1, p.J, g, 2) : -INFINITY;
     nparts = 2;
   }
   __syncthreads();

@@ -289,8 +289,8 @@ lt2exp_tmem_kernel(const __grid_constant__ CUtensorMap tmap_w, const Lt2expParam
       decode(w.tile, r, n0, s0);
       const int kcol = n0 + n;
       const bool col_ok = kcol < p.K;
-      const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + kcol;
-      const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + kcol;
+      const float* a_col = p.a + static_cast<int64_t>(r) * p.a_s0 + static_cast<int64_t>(kcol) * p.a_s2;
+      const float* b_col = p.b + static_cast<int64_t>(r) * p.b_s0 + static_cast<int64_t>(kcol) * p.b_s2;
 
       // Column maxima over the full I and J (see lt2exp_kernel.cuh).
       float* part = mpart + (tcount & 1) * Cfg::MPART;
