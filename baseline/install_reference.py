@@ -26,7 +26,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
-DEFAULT_CHECKOUT = Path(os.environ.get("TRITURUS_REFERENCE_DIR", "/root/reference"))
+# a checkout of the reference next to this repository, unless the environment names another place
+DEFAULT_CHECKOUT = Path(os.environ.get("TRITURUS_REFERENCE_DIR", str(HERE.parent.parent / "reference")))
 
 
 def install(checkout: Path = DEFAULT_CHECKOUT, force: bool = False) -> bool:
