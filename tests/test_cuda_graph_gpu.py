@@ -42,6 +42,34 @@ def test_lm2exp_graph_replay(variant):
     tb.check_status()
 
 
+@pytest.mark.parametrize("variant,precision", [(2567, "tf32"), (402564, "3xtf32"), (301282, "tf32")])
+def test_optimistic_stabilisers_under_graph_replay(variant, precision):
+    """The optimistic forms captured once (the contraction, the flag hand-over and the conditional launches of the
+    exact passes, chained as programmatic dependents) and replayed on inputs that keep the optimistic result, then
+    on inputs that overflow it, then on benign ones again: the flag words live in the workspace the capture holds,
+    are raised and put down by the captured kernels themselves, and every replay is right."""
+    import triturus_b200 as tb
+
+    g = torch.Generator().manual_seed(43)
+    R, I, J, K = 2, 512, 256, 300
+    a = torch.rand(R, I, J, generator=g).cuda()
+    b = torch.randn(R, J, K, generator=g).cuda()
+    graph, out = _capture(lambda x, y: tb.lm2exp(x, y, precision=precision, variant=variant), a, b)
+    ramp = torch.arange(J, dtype=torch.float32).view(1, J, 1) * 2.0  # rows far above the first 32: overflow
+    for step, kind in enumerate(("benign", "overflow", "benign", "overflow", "benign")):
+        g2 = torch.Generator().manual_seed(100 + step)
+        bb = torch.randn(R, J, K, generator=g2) * 3.0
+        if kind == "overflow":
+            bb = bb + ramp
+        a.copy_(torch.rand(R, I, J, generator=g2))
+        b.copy_(bb)
+        graph.replay()
+        torch.cuda.synchronize()
+        res = orc.compare_logspace(out.cpu(), orc.lm2exp_fp64(a.cpu(), b.cpu()), ATOL[precision])
+        assert res["ok"], (kind, step, res)
+    tb.check_status()
+
+
 @pytest.mark.parametrize("mode", ["unsplit", "split"])
 def test_lt2exp_graph_replay(mode):
     """The split mode captures three kernels (zero-fill, slices, log pass)."""
