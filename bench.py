@@ -804,10 +804,10 @@ def main() -> None:
         roof["kernel"] = ("lt2exp_kernel" if wl.op == "lt2exp" else
                           "lm2exp chain link (stabiliser supplied, column maxima returned)" if args.chain else
                           ("colmax_kernel + lm2exp_pair_kernel / lm2exp_kernel" if stab == 1 else
-                           "lm2exp_tspair_kernel with the optimistic stabiliser (+ two conditional launches of the exact "
-                           "passes, which return at once)" if stab == 0 else
-                           "lm2exp_kernel, max pass over the first k-block of each slab (+ flag hand-over and the "
-                           "conditional launch of the full pass, which returns at once)" if stab == 3 else
+                           "lm2exp_tspair_kernel with the optimistic stabiliser (+ the conditional launch of the same kernel "
+                           "with an exact max pass, which returns at once)" if stab == 0 else
+                           "lm2exp_kernel, max pass over the first k-block of each slab (+ the conditional launch of the "
+                           "full pass, which returns at once)" if stab == 3 else
                            "colmax_kernel over the first 32 rows + lm2exp_pair_kernel (+ two conditional launches of "
                            "the exact passes, which return at once)" if stab == 4
                            else "lm2exp_kernel (fused max pass)"))

@@ -145,7 +145,7 @@ def test_chain_launch_counts():
     assert f(32, 1024, 1024, 1024, 0, 0, 1, 0) == 1
     assert f(32, 1024, 1024, 1024, 0, 0, 1, 1) == 2
     assert f(256, 128, 256, 8192, 1, 0, 0, 0) == 1  # fused max pass
-    assert f(256, 128, 256, 8192, 0, 0, 0, 0) == 3  # plain TF32: optimistic max pass + republish + conditional exact launch
+    assert f(256, 128, 256, 8192, 0, 0, 0, 0) == 2  # plain TF32: optimistic max pass + conditional launch of the full one
     assert f(256, 128, 256, 8192, 0, 0, 0, 1) == 1  # returned column maxima: exact pass
     assert f(128, 256, 256, 8192, 0, 0, 1, 1) == 1  # one row tile: maxima stored directly, no fill
     assert f(32, 1024, 1024, 1024, 0, 202561, 1, 0) < 0

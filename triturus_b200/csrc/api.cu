@@ -123,17 +123,6 @@ __global__ void __launch_bounds__(256) rowmax_kernel(const float* __restrict__ x
   if (lane == 0) m[static_cast<int64_t>(r) * K + k] = clamp_stab(mx);
 }
 
-// Between an optimistic single-CTA launch and the conditional exact launch behind it: moves the flag the first
-// one may have raised into the word the second one reads, and puts the flag down for the next call.
-__global__ void republish_flag_kernel(int* flag) {
-  pdl_launch_dependents();
-  pdl_wait();
-  if (threadIdx.x == 0) {
-    flag[1] = flag[0] != 0 ? 1 : 0;
-    flag[0] = 0;
-  }
-}
-
 // Fills m[0..n) with -inf: the start value of the column maxima that an epilogue folds into it.
 __global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* __restrict__ m, int64_t n) {
   for (int64_t i = blockIdx.x * 256 + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) m[i] = -INFINITY;
@@ -348,6 +337,7 @@ static int launch_lm2exp_pair(const CUtensorMap& ta, const CUtensorMap& tb, cons
 //                                  NS NSB groups optimistic
 using LmTsPair = Lm2expTsPairCfg<8, 4, 2>;
 using LmTsPairOpt = Lm2expTsPairCfg<8, 4, 2, true>;
+using LmTsPairFused = Lm2expTsPairCfg<8, 4, 2, false, true>;  // exact max pass inside: the conditional launch behind Opt
 
 // The CTA-pair kernel with the generated operand in tensor memory (plain TF32, a with j contiguous).
 template <class Cfg>
@@ -580,7 +570,7 @@ int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, in
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan);
   if (rc != TRITURUS_B200_OK) return rc;
   // optimistic stabiliser: the contraction and the two conditional launches of the exact passes
-  return plan.fused ? (plan.optimistic_fused ? 3 : 1) : (plan.optimistic ? 3 : (plan.optimistic_prepass ? 4 : 2));
+  return plan.fused ? (plan.optimistic_fused ? 2 : 1) : (plan.optimistic_prepass ? 4 : 2);
 }
 
 int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant) {
@@ -781,11 +771,11 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
     po.opt_flag = flag;
     rc = launch_lm2exp_tspair<LmTsPairOpt>(ta, tb_plain, to, po, st, false);
     if (rc != TRITURUS_B200_OK) return rc;
-    rc = colmax_run(b, m_buf, R, J, K, bstr, stream, flag, flag + 1);
-    if (rc != TRITURUS_B200_OK) return rc;
-    p.only_if = flag + 1;
+    // (the exact column maxima are found inside the conditional kernel: one launch behind the optimistic one)
+    p.m_ws = nullptr;
+    p.only_if = flag;
     p.reset_flag = flag;
-    return launch_lm2exp_tspair<LmTsPair>(ta, tb_plain, to, p, st, true);
+    return launch_lm2exp_tspair<LmTsPairFused>(ta, tb_plain, to, p, st, true);
   }
   if (pair && !use_ts && plan.optimistic_prepass && prepass && ws_flags && out_colmax == nullptr) {
     // Pre-pass over the first 32 rows of b only; the contraction raises the flag if a result overflowed, and the
@@ -851,16 +841,15 @@ static int lm2exp_run_block(const float* a, const float* b, float* out, int64_t 
   };
   if (fused && plan.optimistic_fused && ws_flags && out_colmax == nullptr) {
     // The max pass scans only the first k-block of each slab; a launch that saw a result overflow raises the
-    // flag, one thread moves it to the second word, and the same kernel with the full max pass follows as a
-    // launch that returns at once unless that word is up.
+    // flag, and the same kernel with the full max pass follows as a launch that returns at once unless the flag
+    // is up (its last CTA then puts it down again).
     int* flag = static_cast<int*>(workspace);
     Lm2expParams po = p;
     po.opt_flag = flag;
     rc = single(po, false);
     if (rc != TRITURUS_B200_OK) return rc;
-    rc = launch_maybe_dependent(republish_flag_kernel, dim3(1), 32, 0, st, true, flag);
-    if (rc != TRITURUS_B200_OK) return rc;
-    p.only_if = flag + 1;
+    p.only_if = flag;
+    p.reset_flag = flag;
     return single(p, true);
   }
   return single(p, dep);
@@ -976,7 +965,7 @@ int triturus_b200_lm2exp_chain_launches(int64_t R, int64_t I, int64_t J, int64_t
   Lm2expPlan plan;
   const int rc = plan_lm2exp(R, I, J, K, precision, variant, &plan, have_b_colmax != 0);
   if (rc != TRITURUS_B200_OK) return rc;
-  if ((plan.optimistic || plan.optimistic_fused) && !want_out_colmax) return 3;  // as triturus_b200_lm2exp_launches
+  if ((plan.optimistic || plan.optimistic_fused) && !want_out_colmax) return 2;  // as triturus_b200_lm2exp_launches
   if (plan.optimistic_prepass && !want_out_colmax) return 4;
   return 1 + ((plan.fused || have_b_colmax) ? 0 : 1) + ((want_out_colmax && !plan.colmax_exclusive) ? 1 : 0);
 }

@@ -57,7 +57,8 @@ struct Lm2expParams {
   // The optimistic stabilisers (TMEM-operand pair kernel; fused max pass of the single-CTA kernel):
   const int* only_if = nullptr;  // a conditional launch: the kernel returns at once when *only_if == 0
   int* opt_flag = nullptr;       // optimistic launches set *opt_flag = 1 when a result overflowed
-  int* reset_flag = nullptr;     // a conditional launch that does run puts this word (the flag behind only_if) down
+  int* reset_flag = nullptr;     // a conditional launch that does run puts this flag down: at once when only_if is a
+                                 // republished copy of it (pair kernels), else by its last CTA, counted in reset_flag[1]
 };
 
 // PLAIN_ = true turns the kernel into a plain batched matrix product out = a * b (the reference's `mm`,
@@ -201,6 +202,12 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // the same raises *opt_flag, upon which the caller's conditional launch redoes the call with the full pass.
   const bool opt = fused && p.opt_flag != nullptr;
   const int KBM = opt ? 1 : KB;  // k-blocks of the max pass
+  if (opt) {
+    // the conditional launch behind this one may take its place as this grid's CTAs leave; the word behind the
+    // flag, with which that launch finds its last CTA should it run, is cleared here (nothing else uses it now)
+    pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.opt_flag[1] = 0;
+  }
   // Accumulation chunks per tile and the accumulator buffers they rotate through (see Lm2expCfg::PROMOTE).
   const bool promote = Cfg::PROMOTE && KB > Cfg::CHUNK;
   const int nch = promote ? (KB + Cfg::CHUNK - 1) / Cfg::CHUNK : 1;
@@ -828,6 +835,15 @@ lm2exp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (p.reset_flag != nullptr && threadIdx.x == 0) {
+    // A conditional launch that ran: every CTA read the flag when it started, so the CTA that finishes last puts
+    // it down (the word behind it counts the finished CTAs).
+    __threadfence();
+    if (atomicAdd(p.reset_flag + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.reset_flag[1] = 0;
+      p.reset_flag[0] = 0;
+    }
   }
 }
 

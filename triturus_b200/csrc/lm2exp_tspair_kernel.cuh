@@ -52,7 +52,7 @@ __device__ long long g_timeline[16 * 256];
 // (1-2 us from L2 / HBM) -> transform -> MMA -> commit" is several thousand cycles long, so the number of
 // k-blocks in flight, not any pipe, bounds a single ring of six stages (measured 1 100 cycles per k-block for
 // 512 cycles of MMAs); two rings put 8 + 5 tiles in flight in the same shared memory.
-template <int NS_, int NSB_, int NG_ = 2, bool OPT_ = false>
+template <int NS_, int NSB_, int NG_ = 2, bool OPT_ = false, bool FUSED_ = false>
 struct Lm2expTsPairCfg {
   static constexpr int BM = 128;   // columns k per CTA (256 per pair): TMEM lanes
   static constexpr int BN = 256;   // rows i per pair tile (N of the MMA), 128 per CTA's shared memory
@@ -70,8 +70,15 @@ struct Lm2expTsPairCfg {
   // which fp32 absorbs up to e^88; a result that overflowed all the same (+inf or NaN) raises *opt_flag and the
   // caller's conditional launches redo the call with the exact column maxima.
   static constexpr bool OPT = OPT_;
-  static constexpr int NBAR = 3 * NS + 2 * NSB + 2 + (OPT ? 16 : 0);
-  static constexpr int M_TILE_BYTES = OPT ? 2 * BM * 4 : 0;
+  // FUSED: the exact stabiliser inside the kernel (the conditional launch behind an optimistic one).  Every tile
+  // starts with a max pass: its b tiles stream through ring 2 once more, each transform group keeps the running
+  // maximum of its k-blocks per lane, the groups other than the first hand theirs over through shared memory,
+  // and the first group publishes the column maxima like the optimistic instance publishes its estimate.
+  static constexpr bool FUSED = FUSED_;
+  static constexpr bool SLOTS = OPT || FUSED;  // stabilisers handed from the transform warps to the other roles
+  static_assert(!(OPT && FUSED), "one or the other");
+  static constexpr int NBAR = 3 * NS + 2 * NSB + 2 + (SLOTS ? 16 : 0) + (FUSED ? 4 * (NG - 1) : 0);
+  static constexpr int M_TILE_BYTES = (SLOTS ? 2 * BM * 4 : 0) + (FUSED ? (NG - 1) * BM * 4 : 0);
   static constexpr int SMEM_BYTES = 1024 + NS * A_TILE + NSB * B_TILE + EPI_STAGE + M_TILE_BYTES + NBAR * 8 + 64;
   static_assert(E_COL0 + NS * BK <= TMEM_COLS, "TMEM capacity");
   static_assert(SMEM_BYTES <= 232448, "shared memory capacity");
@@ -100,12 +107,18 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // A conditional launch: runs only if the launch before it raised the flag (same value for every thread of
   // both CTAs, read before any barrier or allocation exists).
   if (p.only_if != nullptr) {
-    pdl_wait();  // the conditional pre-pass before this launch has republished the flag in *only_if
+    pdl_wait();  // (launched as a programmatic dependent of the kernel that may have raised the flag)
     if (*p.only_if == 0) return;
-    if (blockIdx.x == 0 && threadIdx.x == 0 && p.reset_flag != nullptr) *p.reset_flag = 0;  // all its readers are done
+    // (a flag republished in a second word by a conditional pre-pass: all readers of the first one are done)
+    if (!Cfg::FUSED && blockIdx.x == 0 && threadIdx.x == 0 && p.reset_flag != nullptr) *p.reset_flag = 0;
   }
-  // Optimistic instances let the conditional launches behind them take their places as this grid's CTAs leave.
-  if (Cfg::OPT) pdl_launch_dependents();
+  // Optimistic instances let the conditional launch behind them take its place as this grid's CTAs leave, and
+  // clear the counter with which that launch, should it run, finds its last CTA (nothing else uses the word
+  // while this kernel runs).
+  if (Cfg::OPT) {
+    pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.opt_flag[1] = 0;
+  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -121,9 +134,12 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint64_t* b_empty = b_full + NSB;       // [NSB] the four transform warps of the k-block hold it in registers
   uint64_t* acc_full = b_empty + NSB;     // [1] accumulator complete (committed by the leader)
   uint64_t* acc_empty = acc_full + 1;     // [1] (leader's copy is used) epilogues of both CTAs drained it
-  uint64_t* m_ready = acc_empty + 1;      // OPT [2][4] slot, lane quarter: stabilisers written
-  uint64_t* m_free = m_ready + 8;         // OPT [2][4] every reader of the quarter (epilogue warp, other groups) is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1 + (Cfg::OPT ? 16 : 0));
+  uint64_t* m_ready = acc_empty + 1;      // SLOTS [2][4] slot, lane quarter: stabilisers written
+  uint64_t* m_free = m_ready + 8;         // SLOTS [2][4] every reader of the quarter (epilogue warp, other groups) is done
+  uint64_t* part_ready = m_free + 8;      // FUSED [NG - 1][4] group g > 0, lane quarter: its partial maxima written
+  float* m_part = m_tile + 2 * BM;        // FUSED [NG - 1][BM] partial column maxima of the groups other than the first
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1 + (Cfg::SLOTS ? 16 : 0) +
+                                                    (Cfg::FUSED ? 4 * (Cfg::NG - 1) : 0));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -148,11 +164,14 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 8);
-    if (Cfg::OPT) {
+    if (Cfg::SLOTS) {
       for (int i = 0; i < 8; ++i) {
         mbar_init(&m_ready[i], 1);
         mbar_init(&m_free[i], Cfg::NG);  // the epilogue warp and one warp of every other transform group
       }
+    }
+    if (Cfg::FUSED) {
+      for (int i = 0; i < 4 * (Cfg::NG - 1); ++i) mbar_init(&part_ready[i], 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
@@ -212,13 +231,15 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         int r, n0, i0;
         decode(tile, r, n0, i0);
         const int my_n0 = n0 + static_cast<int>(rank) * BM;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % NSB;
-          const uint32_t ph = (it / NSB) & 1;
-          if (!(ok = mbar_wait(&b_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
-          TB200_TL(10, it);
-          mbar_arrive_expect_tx(&b_full[s], Cfg::B_TILE);
-          tma_load_3d(b_tile(s), &tmap_b, &b_full[s], my_n0, kb * BK, r);
+        for (int pass = Cfg::FUSED ? 0 : 1; ok && pass < 2; ++pass) {  // 0 = max pass, 1 = contraction
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % NSB;
+            const uint32_t ph = (it / NSB) & 1;
+            if (!(ok = mbar_wait(&b_empty[s], ph ^ 1, ctl, STATUS_TIMEOUT_PRODUCER))) break;
+            TB200_TL(10, it);
+            mbar_arrive_expect_tx(&b_full[s], Cfg::B_TILE);
+            tma_load_3d(b_tile(s), &tmap_b, &b_full[s], my_n0, kb * BK, r);
+          }
         }
       }
     }
@@ -295,12 +316,12 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int kcol = k0 + lane;
       const bool col_ok = kcol < p.K;
       float m = 0.f;
-      if (!Cfg::OPT && col_ok) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
+      if (!Cfg::SLOTS && col_ok) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
       float* ocol = p.out + static_cast<int64_t>(r) * p.out_s0 + kcol;
       if (!(ok = mbar_wait_warp(acc_full, tcount & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
       if (warp == 4 && lane == 0) TB200_TL(7, tcount);
       tc_fence_after_sync();
-      if (Cfg::OPT) {
+      if (Cfg::SLOTS) {
         // the stabilisers this tile was computed with (written long before the accumulator completed)
         const uint32_t slot = (tcount & 1) * 4 + q;
         if (!(ok = mbar_wait_warp(&m_ready[slot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_EPILOGUE))) break;
@@ -384,7 +405,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t ebase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::E_COL0;
     const uint32_t xf_done_leader0 = map_to_cta(smem_u32(&xf_done[0]), 0);
     pdl_wait();  // m comes from the pre-pass (the producer warp is already loading operand tiles meanwhile)
-    uint32_t it0 = 0, tcount = 0;
+    uint32_t it0 = 0, itb0 = 0, tcount = 0;  // k-blocks of ring 1 / tiles of ring 2 before this tile; tiles seen
     bool ok = true;
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
@@ -392,10 +413,46 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int kcol = n0 + static_cast<int>(rank) * BM + kl;
       // A column past K reads zero-filled values; the stabiliser +inf turns them into exact zeros.
       float m = INFINITY;
-      if (!Cfg::OPT && kcol < p.K) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
+      if (!Cfg::SLOTS && kcol < p.K) m = clamp_stab(__ldg(p.m_ws + static_cast<int64_t>(r) * p.K + kcol));
       const uint32_t mslot = (tcount & 1) * 4 + q;
       float* mdst = m_tile + (tcount & 1) * BM + kl;
-      if (Cfg::OPT && grp != 0) {
+      if (Cfg::FUSED) {
+        // ---- max pass: running maximum of this lane's column over the k-blocks of this group
+        float mx = -INFINITY;
+        for (int kb = grp; kb < KB; kb += Cfg::NG) {
+          const uint32_t itb = itb0 + static_cast<uint32_t>(kb);
+          const int sb = itb % NSB;
+          if (!(ok = mbar_wait_warp(&b_full[sb], (itb / NSB) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          const float* col = reinterpret_cast<const float*>(b_tile(sb)) + kl;
+          const int jrem = p.J - kb * BK;  // rows past J are zero-filled by TMA and must not enter the maximum
+#pragma unroll
+          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, x < jrem ? col[x * BM] : -INFINITY);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&b_empty[sb]);
+        }
+        if (!ok) break;
+        itb0 += static_cast<uint32_t>(KB);
+        if (grp != 0) {
+          // (rewritten only after this warp has seen m_ready of the tile, i.e. after the first group read it)
+          m_part[(grp - 1) * BM + kl] = mx;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&part_ready[(grp - 1) * 4 + q]);
+        } else {
+          for (int g = 1; g < Cfg::NG; ++g) {
+            if (!(ok = mbar_wait_warp(&part_ready[(g - 1) * 4 + q], tcount & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+            mx = fmaxf(mx, m_part[(g - 1) * BM + kl]);
+          }
+          if (!ok) break;
+          m = (kcol < p.K) ? clamp_stab(mx) : INFINITY;
+          if (tcount >= 2) {
+            if (!(ok = mbar_wait_warp(&m_free[mslot], ((tcount >> 1) - 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+          }
+          *mdst = m;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&m_ready[mslot]);
+        }
+      }
+      if (Cfg::SLOTS && grp != 0) {
         // the group of k-block 0 publishes the tile's stabilisers
         if (!(ok = mbar_wait_warp(&m_ready[mslot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
         m = *mdst;
@@ -406,8 +463,9 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const uint32_t it = it0 + static_cast<uint32_t>(kb);
         const int s = it % NS;
         const uint32_t ph = (it / NS) & 1;
-        const int sb = it % NSB;
-        if (!(ok = mbar_wait_warp(&b_full[sb], (it / NSB) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+        const uint32_t itb = itb0 + static_cast<uint32_t>(kb);
+        const int sb = itb % NSB;
+        if (!(ok = mbar_wait_warp(&b_full[sb], (itb / NSB) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
         if (warp == 8 && lane == 0) TB200_TL(2, it);
         const float* col = reinterpret_cast<const float*>(b_tile(sb)) + kl;
         float v[32];
@@ -452,6 +510,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (warp == 8 && lane == 0) TB200_TL(6, it);
       }
       it0 += static_cast<uint32_t>(KB);
+      itb0 += static_cast<uint32_t>(KB);
     }
   }
 
@@ -468,6 +527,15 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (Cfg::FUSED && p.reset_flag != nullptr && threadIdx.x == 0) {
+    // A conditional launch that ran: every CTA read the flag when it started, so the CTA that finishes last may
+    // put it down (the word behind it counts the finished CTAs; the optimistic launch before this one cleared it).
+    __threadfence();
+    if (atomicAdd(p.reset_flag + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.reset_flag[1] = 0;
+      p.reset_flag[0] = 0;
+    }
   }
 }
 
