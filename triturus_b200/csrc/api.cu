@@ -1059,7 +1059,11 @@ static int launch_lt2exp_with(const CUtensorMap& tw, Lt2expParams p, const LtLau
   const bool have_ws = CAN_PARK && sm_count() * sizeof(int) <= kParkHeader &&
                        (L.query != nullptr || (L.ws != nullptr && L.ws_bytes >= park_need &&
                                                (reinterpret_cast<uintptr_t>(L.ws) & 255) == 0));
-  const LtSplit sp = lt2exp_split(nt, p.I, p.J, L.split_request, have_ws);
+  // Not chosen automatically for a launch that re-sums its accumulator in chunks (3xTF32, long plain-TF32
+  // contractions): sharing tiles made those slower (R32 256^4: 1.32 against 0.81 ms in TF32, 2.87 against 1.68 ms
+  // in 3xTF32; R128: 2.75 against 2.40 ms), the explicit request 9998 still selects it.
+  const bool chunked = Cfg::PROMOTE && static_cast<int64_t>((p.J + 31) / 32) * p.I > Cfg::CHUNK;
+  const LtSplit sp = lt2exp_split(nt, p.I, p.J, L.split_request, have_ws && !chunked);
   p.nsplit = sp.nsplit;
   p.stream = sp.stream;
   const int64_t items = nt * sp.nsplit;

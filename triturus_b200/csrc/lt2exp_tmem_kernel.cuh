@@ -39,6 +39,8 @@ struct Lt2expTmemCfg {
   static constexpr int NB = NB_;           // 128-column blocks per tile: each is one M = 128 MMA on the same w tile
   static constexpr int BN = 128 * NB;      // columns k per tile
   static constexpr int MT = MT_, NS = NS_, PREC = 0, NTW = 8;
+  static constexpr bool PROMOTE = false;  // no chunked re-summation of the accumulator in these kernels
+  static constexpr int CHUNK = 1 << 30;
   static constexpr int W_TILE = BM * BK * 4;
   static constexpr int STAGE = MT * W_TILE;
   static constexpr int BLK_COLS = MT * BM;        // accumulator columns of one column block
