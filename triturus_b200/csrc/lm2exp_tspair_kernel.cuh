@@ -308,7 +308,8 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     pdl_wait();  // m comes from the pre-pass, which may still be running when this kernel starts
     uint32_t tcount = 0;
     bool ok = true;
-    bool overflowed = false;  // OPT: some result of this lane came out +inf or NaN
+    uint32_t acc_max = 0;  // OPT: largest accumulator bit pattern of this lane (sums of non-negative products, so
+                           // +inf and NaN are exactly the patterns >= 0x7f800000 read as unsigned)
     for (int tile = pair; ok && tile < p.num_tiles; tile += npairs, ++tcount) {
       int r, n0, i0;
       decode(tile, r, n0, i0);
@@ -368,7 +369,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 const float o = m + lg2_approx(__uint_as_float(v[h][e])) * LN2_F;
-                if (Cfg::OPT) overflowed |= !(o < INFINITY);
+                if (Cfg::OPT) acc_max = max(acc_max, v[h][e]);
                 *reinterpret_cast<float*>(stg + sw128_offset(e, lane)) = o;
               }
               fence_proxy_async_smem();
@@ -384,7 +385,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 const float o = m + lg2_approx(__uint_as_float(v[h][e])) * LN2_F;
-                if (Cfg::OPT) overflowed |= !(o < INFINITY);
+                if (Cfg::OPT) acc_max = max(acc_max, v[h][e]);
                 if (col_ok && e < nrows) orow[static_cast<int64_t>(e) * p.out_s1] = o;
               }
             }
@@ -395,7 +396,7 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     if (use_tma && lane == 0) tma_store_wait_all();  // shared memory must outlive the last box
     if (Cfg::OPT) {
-      if (__any_sync(0xffffffffu, overflowed) && lane == 0) *p.opt_flag = 1;
+      if (__any_sync(0xffffffffu, acc_max >= 0x7f800000u) && lane == 0) *p.opt_flag = 1;
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ transform: b tile -> E^T in tensor memory
@@ -452,12 +453,20 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (lane == 0) mbar_arrive(&m_ready[mslot]);
         }
       }
-      if (Cfg::SLOTS && grp != 0) {
-        // the group of k-block 0 publishes the tile's stabilisers
-        if (!(ok = mbar_wait_warp(&m_ready[mslot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM))) break;
+      // The group of k-block 0 publishes the tile's stabilisers; the other groups pick them up.  In the optimistic
+      // instance that is done after the loads of the group's own first k-block are in flight (the first group
+      // publishes as soon as it holds k-block 0, i.e. at about the same time), not before them.
+      bool need_m = Cfg::SLOTS && grp != 0;
+      auto fetch_m = [&]() -> bool {
+        if (!mbar_wait_warp(&m_ready[mslot], (tcount >> 1) & 1, ctl, STATUS_TIMEOUT_TRANSFORM)) return false;
         m = *mdst;
         __syncwarp();
         if (lane == 0) mbar_arrive(&m_free[mslot]);
+        need_m = false;
+        return true;
+      };
+      if (need_m && Cfg::FUSED) {
+        if (!(ok = fetch_m())) break;
       }
       for (int kb = grp; kb < KB; kb += Cfg::NG) {
         const uint32_t it = it0 + static_cast<uint32_t>(kb);
@@ -472,6 +481,9 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int x = 0; x < 32; ++x) v[x] = col[x * BM];
         const int jrem = p.J - kb * BK;
+        if (need_m) {
+          if (!(ok = fetch_m())) break;
+        }
         if (Cfg::OPT && kb == 0) {
           // (grp == 0) stabiliser = maximum over the first k-block; the slot's readers of two tiles ago are done
           float mx = -INFINITY;
@@ -508,6 +520,9 @@ lm2exp_tspair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(xf_done_leader0 + static_cast<uint32_t>(s) * 8u);
         if (warp == 8 && lane == 0) TB200_TL(6, it);
+      }
+      if (need_m) {  // (a group without a k-block in this tile still reads and releases the slot)
+        if (!(ok = fetch_m())) break;
       }
       it0 += static_cast<uint32_t>(KB);
       itb0 += static_cast<uint32_t>(KB);
