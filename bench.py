@@ -107,8 +107,8 @@ def plan_code(wl, precision: str, variant: int) -> int:
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) taken from
 # the committed ncu summaries under profiles/; None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    ("cfg2", "tf32"): 270.19e6 + 100.37e6,   # profiles/lm2exp_tspair_kernel_cfg2.md
-    ("cfg3", "tf32"): 1107.37e6 + 1016.23e6,  # profiles/lm2exp_tspair_kernel_cfg3.md
+    ("cfg2", "tf32"): 272.34e6 + 100.83e6,   # profiles/lm2exp_tspair_kernel_cfg2.md
+    ("cfg3", "tf32"): 1107.41e6 + 1016.16e6,  # profiles/lm2exp_tspair_kernel_cfg3.md
     ("cfg5", "tf32"): 1999.31e6 + 237.76e6,   # profiles/lt2exp_kernel_cfg5.md
 }
 
