@@ -73,30 +73,29 @@ const char* triturus_b200_strerror(int code);
  *              optimistic stabiliser is then not used.  Keep the workspace between calls (or zero its first
  *              8 bytes once): flag words that are up by accident cost a call the exact passes.
  *
- * Optimistic stabiliser (variant 2567; chosen automatically for plain TF32 on pair tiles when a has j
- * contiguous): no pre-pass over b.  The contraction kernel takes as stabiliser of a column the maximum over its
- * first 32 rows j; later values may exceed it, exp(b - m) is then larger than 1, which fp32 holds up to e^88.
- * Only the stabiliser differs from the exact form, so results agree with it to rounding.  A result that
- * overflowed all the same (+inf or NaN) raises the flag word, and the exact form (the same kernel with a max pass
- * over all of b inside) follows in the stream as a launch that returns at once while the flag is down; when it
- * runs it redoes the whole call and its last CTA puts the flag down again (a flag word that is up by accident
- * in fresh memory costs one exact pass).  Inputs
- * whose columns grow by more than ~80 after their first 32 rows therefore cost a second pass.  The single-CTA
- * kernel has the same form for its fused max pass (STAB = 3; automatic for plain TF32 when the contraction has
- * four k-blocks or more and the launch more than one wave of tiles): the pass scans one k-block instead of the
- * whole slab, and the same kernel with the full pass follows as the conditional launch.  The shared-memory pair kernel (tile 2564; the automatic choice in
- * 3xTF32) has it as STAB = 4: the pre-pass launch scans 32 rows instead of J, then the contraction and the two
- * conditional launches (4 in all).  None of the three is used when column maxima of the result are requested.
- * The reference
- * finds the exact maximum in a first loop over j inside its kernel (triturus/lm2exp.py:124-127).
+ * Optimistic stabiliser (variant 2567; chosen automatically for plain TF32 on pair tiles, i.e. I > 128, when a has
+ * j contiguous and the call has at least 2e10 FLOP): no pre-pass over b.  The contraction kernel takes as
+ * stabiliser of a column the maximum over its first 32 rows j; later values may exceed it, exp(b - m) is then
+ * larger than 1, which fp32 holds up to e^88.  Only the stabiliser differs from the exact form, so results agree
+ * with it to rounding.  A result that overflowed all the same (+inf or NaN) raises the flag word, and the exact
+ * form (the same kernel with a max pass over all of b inside) follows in the stream as a launch that returns at
+ * once while the flag is down; when it runs it redoes the whole call and its last CTA puts the flag down again (a
+ * flag word that is up by accident in fresh memory costs one exact pass).  Inputs whose columns grow by more
+ * than ~80 after their first 32 rows therefore cost a second pass.
+ * The single-CTA kernel has the same form for its fused max pass (STAB = 3; automatic for plain TF32 when one
+ * 128-row block covers I, the contraction has four k-blocks or more, the launch more than one wave of tiles and
+ * 2e10 FLOP): the pass scans one k-block instead of the whole slab, and the same kernel with the full pass
+ * follows as the conditional launch.  The shared-memory pair kernel (tile 2564; the automatic choice in 3xTF32,
+ * with the same size rule) has it as STAB = 4: the pre-pass launch scans 32 rows instead of J, then the
+ * contraction and two conditional launches (full pre-pass, contraction), 4 in all.  None of the three is used
+ * when column maxima of the result are requested or a stabiliser is supplied.  The reference finds the exact
+ * maximum in a first loop over j inside its kernel (triturus/lm2exp.py:124-127).
  */
 size_t triturus_b200_lm2exp_workspace_bytes(int64_t R, int64_t I, int64_t J, int64_t K);
 /* Number of kernels one triturus_b200_lm2exp_f32 call launches for these arguments on the current device:
  * 2 (stabiliser pre-pass + contraction; or an optimistic kernel + its conditional launch), 1 (fused max pass) or
  * 4 (optimistic 32-row pre-pass, contraction, and two conditional launches; a with j contiguous and a full-size
- * workspace assumed);
- * negative on invalid arguments.  The reference
- * has no counterpart (its launch count is Triton's business, triturus/lm2exp.py:186-205). */
+ * workspace assumed); negative on invalid arguments.  The reference has no counterpart (its launch count is Triton's business, triturus/lm2exp.py:186-205). */
 int triturus_b200_lm2exp_launches(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lm2exp_f32(const float* a, const float* b, float* out, int64_t R, int64_t I, int64_t J, int64_t K,
                              const int64_t a_strides[3], const int64_t b_strides[3], const int64_t out_strides[3],
