@@ -229,3 +229,28 @@ def test_host_pipeline_chunking():
         check(chunk_bounds(batch, 12 << 20), batch)
     with pytest.raises(ValueError):
         chunk_bounds(0, 4)
+
+
+def test_operand_preparation_rules():
+    """Which lm2exp operands the wrapper passes as they are and which it copies (pure host logic, CPU tensors)."""
+    x = torch.zeros(2, 64, 96)
+    assert _native._tma_ok(x)
+    assert not _native._tma_ok(x[:, :, ::2])          # innermost stride 2
+    assert not _native._tma_ok(torch.zeros(2, 64, 97))  # row pitch not a multiple of 4 elements
+    assert _native._tma_ok(torch.zeros(1, 1, 97))     # strides of size-1 dimensions do not matter
+    assert _native._tma_ready(x) is x
+    padded = _native._tma_ready(torch.ones(2, 5, 7))
+    assert padded.shape == (2, 5, 7) and padded.stride() == (40, 8, 1) and bool((padded == 1).all())
+    # b: plain, transposed (j contiguous), odd
+    b_t = torch.zeros(2, 96, 64).transpose(1, 2)      # [R, J=64, K=96] with stride 1 along j
+    assert _native._lm2exp_b_operand(b_t, 0) is b_t
+    assert _native._lm2exp_b_operand(b_t, 1282) is b_t
+    assert _native._lm2exp_b_operand(b_t, 2564) is not b_t      # pair tile: copy
+    assert _native._lm2exp_b_operand(b_t, 201281) is not b_t    # fused max pass: copy
+    b_odd = torch.zeros(2, 64, 97)
+    assert _native._lm2exp_b_operand(b_odd, 0, flop=1e6) is b_odd          # small problem: in place
+    assert _native._lm2exp_b_operand(b_odd, 0, flop=1e12) is not b_odd     # large problem: padded copy
+    assert _native._lm2exp_b_operand(b_odd, 2564, flop=1e6) is not b_odd   # pair tile asked for: copy
+    assert _native._lm2exp_b_operand(b_odd, 0, flop=1e6, want_colmax=True) is not b_odd
+    assert _native._in_place_small(b_odd, 1e6, 0, False) and not _native._in_place_small(b_odd, 1e12, 0, False)
+    assert not _native._in_place_small(b_odd.double(), 1e6, 0, False)
