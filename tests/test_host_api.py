@@ -254,3 +254,19 @@ def test_operand_preparation_rules():
     assert _native._lm2exp_b_operand(b_odd, 0, flop=1e6, want_colmax=True) is not b_odd
     assert _native._in_place_small(b_odd, 1e6, 0, False) and not _native._in_place_small(b_odd, 1e12, 0, False)
     assert not _native._in_place_small(b_odd.double(), 1e6, 0, False)
+
+
+def test_automatic_plans_of_lm2exp():
+    """What a call runs for the benchmark shapes and around the size rule of the optimistic stabilisers (the plan
+    queries need no GPU: without one they assume 148 SMs)."""
+    plan, launches = _native.LIB.triturus_b200_lm2exp_plan, _native.LIB.triturus_b200_lm2exp_launches
+    assert plan(32, 1024, 1024, 1024, 0, 0) == 2567 and launches(32, 1024, 1024, 1024, 0, 0) == 2      # cfg2, TF32
+    assert plan(32, 1024, 1024, 1024, 1, 0) == 402564 and launches(32, 1024, 1024, 1024, 1, 0) == 4    # cfg2, 3xTF32
+    assert plan(128, 256, 256, 8192, 0, 0) == 2567                                                      # cfg3
+    assert plan(4, 256, 256, 256, 0, 0) == 201281 and launches(4, 256, 256, 256, 0, 0) == 1             # cfg1
+    assert plan(64, 256, 256, 256, 0, 0) // 100000 == 2      # two row blocks but under 2e10 FLOP: one fused launch
+    assert plan(256, 128, 256, 8192, 0, 0) // 100000 == 3    # one row block, long launch: optimistic fused max pass
+    assert plan(4, 1024, 1024, 1024, 0, 0) == 102566         # a chunk of the host pipeline: pre-pass + pair kernel
+    assert plan(32, 1024, 1024, 1024, 0, 100000) == 102566   # forced pre-pass
+    assert plan(32, 1024, 1024, 1024, 0, 2564) == 102564     # explicit tiles keep the exact stabiliser
+    assert plan(32, 1024, 1024, 1024, 0, 402567) < 0 and plan(32, 1024, 1024, 1024, 1, 2567) < 0
