@@ -162,8 +162,9 @@ int triturus_b200_lt2exp_launches(int64_t R, int64_t S, int64_t I, int64_t J, in
  * wave shared).  The counterpart of reading the reference's autotuner choice (triturus/lt2exp.py:9-75,78-222); negative
  * on invalid arguments. */
 int triturus_b200_lt2exp_plan(int64_t R, int64_t S, int64_t I, int64_t J, int64_t K, int precision, int variant);
-/* The same for triturus_b200_lm2exp_f32: STAB * 100000 + BN * 10 + MT with STAB = 1 (pre-pass) or 2 (fused max
- * pass); negative on invalid arguments. */
+/* The same for triturus_b200_lm2exp_f32: STAB * 100000 + BN * 10 + MT with STAB = 1 (pre-pass), 2 (fused max
+ * pass), 3 or 4 (their optimistic forms); the tile code 2567 stands by itself (its stabiliser is part of the
+ * tile).  Negative on invalid arguments. */
 int triturus_b200_lm2exp_plan(int64_t R, int64_t I, int64_t J, int64_t K, int precision, int variant);
 int triturus_b200_lt2exp_f32(const float* w, const float* a, const float* b, float* out, int64_t R, int64_t S,
                              int64_t I, int64_t J, int64_t K, const int64_t w_strides[4], const int64_t a_strides[3],

@@ -270,3 +270,56 @@ def test_automatic_plans_of_lm2exp():
     assert plan(32, 1024, 1024, 1024, 0, 100000) == 102566   # forced pre-pass
     assert plan(32, 1024, 1024, 1024, 0, 2564) == 102564     # explicit tiles keep the exact stabiliser
     assert plan(32, 1024, 1024, 1024, 0, 402567) < 0 and plan(32, 1024, 1024, 1024, 1, 2567) < 0
+
+
+def test_plans_over_random_shapes_are_consistent():
+    """Invariants of the automatic plans over a few thousand random shapes (no GPU needed): the code decodes to a
+    known tile and stabiliser, pins itself (asked for as an explicit variant it comes back unchanged), agrees with
+    the launch count, and takes the optimistic forms only from 2e10 FLOP on."""
+    import random
+
+    rnd = random.Random(5)
+    lm_plan, lm_launches = _native.LIB.triturus_b200_lm2exp_plan, _native.LIB.triturus_b200_lm2exp_launches
+    lt_plan, lt_launches = _native.LIB.triturus_b200_lt2exp_plan, _native.LIB.triturus_b200_lt2exp_launches
+    dims = [1, 3, 31, 32, 33, 64, 100, 127, 128, 129, 200, 256, 257, 384, 512, 1000, 1024, 2048, 4096, 8192]
+    for _ in range(3000):
+        R = rnd.choice([1, 2, 4, 7, 16, 32, 64, 128, 384])
+        I, J, K = rnd.choice(dims), rnd.choice(dims), rnd.choice(dims)
+        prec = rnd.choice([0, 1])
+        code, n = lm_plan(R, I, J, K, prec, 0), lm_launches(R, I, J, K, prec, 0)
+        assert code > 0, (R, I, J, K, prec, code)
+        stab, tile = code // 100000, code % 100000
+        assert tile in (1281, 1282, 2561, 2562, 2564, 2566, 2567), (R, I, J, K, prec, code)
+        if tile in (2566, 2567):
+            assert prec == 0 and I > 128, (R, I, J, K, code)
+        if tile == 2567:
+            assert stab == 0 and n == 2
+        else:
+            assert stab in (1, 2, 3, 4) and n == {1: 2, 2: 1, 3: 2, 4: 4}[stab], (R, I, J, K, prec, code, n)
+        if tile == 2567 or stab in (3, 4):
+            assert 2.0 * R * I * J * K >= 2e10, (R, I, J, K, prec, code)
+        if stab == 4:
+            assert tile == 2564
+        if stab in (2, 3):
+            assert tile in (1281, 1282, 2561, 2562)
+        assert lm_plan(R, I, J, K, prec, code) == code, (R, I, J, K, prec, code)
+        assert lm_launches(R, I, J, K, prec, code) == n
+
+    for _ in range(3000):
+        R = rnd.choice([1, 2, 4, 16, 64, 128])
+        S = rnd.choice(dims[:-2])
+        I, J = rnd.choice(dims[:14]), rnd.choice(dims[:14])
+        K = rnd.choice(dims)
+        prec = rnd.choice([0, 1])
+        code, n = lt_plan(R, S, I, J, K, prec, 0), lt_launches(R, S, I, J, K, prec, 0)
+        assert code > 0, (R, S, I, J, K, prec, code)
+        split, tile = code // 10000, code % 10000
+        assert tile in (1281, 1282, 2561, 2562, 1283, 1284, 1285), (R, S, I, J, K, prec, code)
+        if tile in (1283, 1284, 1285):
+            assert prec == 0
+        assert split == 9998 or 1 <= split <= 4096, (R, S, I, J, K, prec, code)
+        if split == 9998:  # shared last wave: in place (1 launch) or through zero-fill and log pass (3)
+            assert n in (1, 3)
+        else:
+            assert n == (1 if split == 1 else 3), (R, S, I, J, K, prec, code, n)
+        assert lt_plan(R, S, I, J, K, prec, code) == code, (R, S, I, J, K, prec, code)
